@@ -132,3 +132,78 @@ class GPT2Config(ModelConfig):
         if self.scale_attn_by_inverse_layer_idx:
             scale /= float(layer + 1)
         return scale
+
+
+def _require_number(value: Any, name: str, positive: bool = False) -> float:
+    if isinstance(value, bool) or not isinstance(value, (int, float)) or not math.isfinite(value):
+        raise ConfigError(f"{name} must be a finite number, got {value!r}")
+    if positive and value <= 0:
+        raise ConfigError(f"{name} must be positive, got {value}")
+    return float(value)
+
+
+_RAKALIX_MIXERS = {"latent_attention": ("heads", "dim", "rot_dim", "vdim", "kv_rank"),
+                   "hgrn2": ("heads", "dim", "vdim")}
+
+
+@dataclass(frozen=True)
+class RakalixConfig(ModelConfig):
+    """Rakalix: ``layers`` lists the layers in order, each {"type": which mixer, "mixer": its sizes
+    and constants, "mlp": {"kind": "dense", "ff": n} or null}; ``norm.eps``, ``canon.taps``
+    (the taps of the convolution over time in front of every sublayer), ``embedding.scale`` and
+    ``residual_mult`` are the model-wide constants.  The document names the design under
+    ``architecture``.  The model has no position limit of its own."""
+
+    ARCHITECTURE: ClassVar[str] = "Rakalix"
+
+    vocab: int = 0
+    width: int = 0
+    layers: tuple = ()
+    norm: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"eps": 1e-6})
+    canon: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"taps": 4})
+    embedding: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"scale": 1.0})
+    residual_mult: float = 1.0
+
+    def __post_init__(self) -> None:
+        _require_int(self.vocab, "vocab")
+        _require_int(self.width, "width")
+        if not isinstance(self.layers, (list, tuple)) or not self.layers:
+            raise ConfigError("layers must be a non-empty list")
+        object.__setattr__(self, "layers", tuple(self.layers))
+        _require_number(self.norm.get("eps"), "norm.eps", positive=True)
+        _require_int(self.canon.get("taps"), "canon.taps")
+        _require_number(self.embedding.get("scale"), "embedding.scale")
+        _require_number(self.residual_mult, "residual_mult")
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, Mapping) else None
+            if kind not in _RAKALIX_MIXERS:
+                raise ConfigError(f"layers[{i}].type must be one of {sorted(_RAKALIX_MIXERS)}, got {kind!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, Mapping):
+                raise ConfigError(f"layers[{i}].mixer must give the mixer's sizes")
+            for key in _RAKALIX_MIXERS[kind]:
+                _require_int(mixer.get(key), f"layers[{i}].mixer.{key}")
+            if kind == "latent_attention":
+                _require_number(mixer.get("scale"), f"layers[{i}].mixer.scale")
+                rot = mixer.get("rot")
+                if not isinstance(rot, Mapping):
+                    raise ConfigError(f"layers[{i}].mixer.rot must give the rotation's constants")
+                dims = _require_int(rot.get("dims"), f"layers[{i}].mixer.rot.dims")
+                _require_number(rot.get("base"), f"layers[{i}].mixer.rot.base", positive=True)
+                if dims % 2 or dims > mixer["rot_dim"]:
+                    raise ConfigError(f"layers[{i}].mixer.rot.dims must be even and at most rot_dim")
+                scaling = rot.get("scaling")
+                if scaling is not None:
+                    for key in ("factor", "original", "fast", "slow"):
+                        _require_number(scaling.get(key) if isinstance(scaling, Mapping) else None,
+                                        f"layers[{i}].mixer.rot.scaling.{key}", positive=True)
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind") != "dense":
+                    raise ConfigError(f"layers[{i}].mlp.kind must be 'dense' (or mlp null), got {mlp!r}")
+                _require_int(mlp.get("ff"), f"layers[{i}].mlp.ff")
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+                "layers": [json.loads(json.dumps(layer)) for layer in self.layers], "norm": dict(self.norm),
+                "canon": dict(self.canon), "embedding": dict(self.embedding), "residual_mult": self.residual_mult}

@@ -1,0 +1,313 @@
+// Root-mean-square norms and what rides on them: plain RMS norm of float32 rows (optionally
+// gathered, optionally rows of a wider matrix), RMS norm fused with a short causal convolution
+// over time whose last inputs live in a request's state slot, the RMS-normed sublayer output
+// added to the residual stream, and the PolyNorm activation.  Statistics, weights and sums are
+// 32-bit throughout; only the stored result may be bfloat16.
+//
+// "RMS norm" is x / sqrt(mean(x^2) + eps), eps inside the root.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 128;
+
+__device__ __forceinline__ float block_sum_128(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  return (red[0] + red[1]) + (red[2] + red[3]);      // the same order in every thread
+}
+
+// Three sums at once (PolyNorm's three powers, or the statistics of several rows).
+template <int N>
+__device__ __forceinline__ void block_sums_128(float (&v)[N], float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = warp_sum(v[i]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) red[i * 4 + warp] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = (red[i * 4] + red[i * 4 + 1]) + (red[i * 4 + 2] + red[i * 4 + 3]);
+}
+
+// ----------------------------------------------------------------- rmsnorm --
+// out[r, :] = x[src(r), :d] / rms * w.  One block per row.
+template <typename O>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_kernel(O* __restrict__ out, long long out_stride, const float* __restrict__ x, long long x_stride,
+               const float* __restrict__ w, const int* __restrict__ rows, int d, float eps) {
+  __shared__ float red[4];
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const int src_row = rows ? rows[r] : r;
+  pdl_wait();
+  const float* src = x + (size_t)src_row * x_stride;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float v = src[i];
+    s = fmaf(v, v, s);
+  }
+  const float inv = 1.0f / sqrtf(block_sum_128(s, red) / (float)d + eps);
+  O* dst = out + (size_t)r * out_stride;
+  for (int i = threadIdx.x; i < d; i += THREADS) dst[i] = from_float<O>(src[i] * inv * (w ? w[i] : 1.0f));
+}
+
+// ------------------------------------------------- rmsnorm + time convolution --
+// h_t = rmsnorm(x_t) * w;  out_t = h_t + sum_j c[:, j] * h_(t - taps + 1 + j), where inputs from
+// before the row's portion come from the request's state (the last taps - 1 inputs h of earlier
+// steps, oldest first; zeros for a new request) and inputs inside the portion are normed again
+// from x.  One block per row.  ``inline_state``: every request of the step brings one row, and the
+// block shifts the request's state itself (each thread owns its channels, so nothing races);
+// otherwise conv_state_kernel runs afterwards.
+constexpr int MAX_TAPS = 8;
+
+template <typename O>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                    const float* __restrict__ taps_w, float* __restrict__ state, const int* __restrict__ row_req,
+                    const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps,
+                    int inline_state) {
+  __shared__ float red[4 * MAX_TAPS];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int req = row_req[t];
+  const int first = req_q_start[req];
+  const int slot = req_slot[req];
+  pdl_wait();
+  const int back = taps - 1;
+  // statistics of this row and of the earlier rows of the portion that the taps reach
+  float sums[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) sums[j] = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+      const int s = t - j;                       // j rows back
+      if (j <= back && s >= first) {
+        const float v = x[(size_t)s * d + i];
+        sums[j] = fmaf(v, v, sums[j]);
+      }
+    }
+  }
+  block_sums_128<MAX_TAPS>(sums, red);
+  float inv[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) inv[j] = 1.0f / sqrtf(sums[j] / (float)d + eps);
+  float* st = state + (size_t)slot * back * d;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float wi = w[i];
+    const float h0 = x[(size_t)t * d + i] * inv[0] * wi;
+    float acc = h0 * (1.0f + taps_w[(size_t)i * taps + back]);
+    float held[MAX_TAPS];                        // the state's values of this channel (inline update)
+#pragma unroll
+    for (int j = 1; j < MAX_TAPS; ++j) {
+      if (j <= back) {
+        const int s = t - j;
+        float hv;
+        if (s >= first) hv = x[(size_t)s * d + i] * inv[j] * wi;
+        else hv = st[(size_t)(back + (s - first)) * d + i];      // s - first in [-back, -1]
+        held[j] = hv;
+        acc = fmaf(taps_w[(size_t)i * taps + back - j], hv, acc);
+      }
+    }
+    out[(size_t)t * d + i] = from_float<O>(acc);
+    if (inline_state) {
+      // one row per request: the new state is the old one shifted by one, this row's h last
+#pragma unroll
+      for (int j = MAX_TAPS - 1; j >= 2; --j)
+        if (j <= back) st[(size_t)(back - j) * d + i] = held[j - 1];
+      if (back >= 1) st[(size_t)(back - 1) * d + i] = h0;
+    }
+  }
+}
+
+// The state after a step: the last taps - 1 of (old state, the portion's inputs h).  One block
+// per request; a thread reads what it needs of its channels before it writes them.
+__global__ void __launch_bounds__(THREADS)
+conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, const float* __restrict__ w,
+                  const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps) {
+  __shared__ float red[4 * MAX_TAPS];
+  pdl_trigger();
+  const int req = blockIdx.x;
+  const int first = req_q_start[req], n = req_q_start[req + 1] - first;
+  const int slot = req_slot[req];
+  pdl_wait();
+  const int back = taps - 1;
+  float sums[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) sums[j] = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+      const int k = n - 1 - j;                   // j rows before the portion's end
+      if (j < back && k >= 0) {
+        const float v = x[(size_t)(first + k) * d + i];
+        sums[j] = fmaf(v, v, sums[j]);
+      }
+    }
+  }
+  block_sums_128<MAX_TAPS>(sums, red);
+  float* st = state + (size_t)slot * back * d;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    float fresh[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+      if (j < back) {
+        const int k = n - 1 - j;
+        if (k >= 0) fresh[j] = x[(size_t)(first + k) * d + i] * (1.0f / sqrtf(sums[j] / (float)d + eps)) * w[i];
+        else fresh[j] = st[(size_t)(back - 1 - j + n) * d + i];     // still an old input: index back + k
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j)
+      if (j < back) st[(size_t)(back - 1 - j) * d + i] = fresh[j];
+  }
+}
+
+// ------------------------------------------------------ normed residual sum --
+// x[t, :] += mult * y[t, :] / rms(y[t, :]) * w
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w, int d,
+                        float eps, float mult) {
+  __shared__ float red[4];
+  pdl_trigger();
+  pdl_wait();
+  const float* src = y + (size_t)blockIdx.x * d;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float v = src[i];
+    s = fmaf(v, v, s);
+  }
+  const float inv = 1.0f / sqrtf(block_sum_128(s, red) / (float)d + eps);
+  float* dst = x + (size_t)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += THREADS) dst[i] += mult * (src[i] * inv * w[i]);
+}
+
+// ---------------------------------------------------------------- polynorm --
+// out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e over a row of width n.
+template <typename I, typename O>
+__global__ void __launch_bounds__(THREADS)
+polynorm_kernel(O* __restrict__ out, const I* __restrict__ z, const float* __restrict__ coeff, int n, float eps) {
+  __shared__ float red[12];
+  pdl_trigger();
+  const float a = coeff[0], b = coeff[1], c = coeff[2], e = coeff[3];
+  pdl_wait();
+  const I* src = z + (size_t)blockIdx.x * n;
+  float s[3] = {0.f, 0.f, 0.f};
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    const float v = to_float<I>(src[i]);
+    const float v2 = v * v, v3 = v2 * v;
+    s[0] += v2;
+    s[1] = fmaf(v2, v2, s[1]);
+    s[2] = fmaf(v3, v3, s[2]);
+  }
+  block_sums_128<3>(s, red);
+  const float i1 = a / sqrtf(s[0] / (float)n + eps);
+  const float i2 = b / sqrtf(s[1] / (float)n + eps);
+  const float i3 = c / sqrtf(s[2] / (float)n + eps);
+  O* dst = out + (size_t)blockIdx.x * n;
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    const float v = to_float<I>(src[i]);
+    const float v2 = v * v;
+    dst[i] = from_float<O>(fmaf(v, i1, fmaf(v2, i2, fmaf(v2 * v, i3, e))));
+  }
+}
+
+// ------------------------------------------------------------ scaled embed --
+template <typename W>
+__global__ void embed_scaled_kernel(float* __restrict__ out, const int* __restrict__ tok, const W* __restrict__ table,
+                                    int d, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  const W* e = table + (size_t)tok[blockIdx.x] * d;
+  float* o = out + (size_t)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float<W>(e[i]) * scale;
+}
+
+}  // namespace
+
+// out[r, :d] = rmsnorm(x[rows ? rows[r] : r, :d]) * w (w null: no weight).  x rows lie x_stride
+// floats apart, out rows out_stride elements.
+AYK_EXPORT int ayk_rmsnorm(void* out, long long out_stride, const float* x, long long x_stride, const float* w,
+                           const int* rows, int n_rows, int d, float eps, int out_dtype, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AYK_REQUIRE(d >= 1, "ayk_rmsnorm: width %d", d);
+  if (out_dtype == AYK_DTYPE_F32)
+    ayk_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(THREADS), 0, stream, (float*)out, out_stride, x, x_stride, w, rows, d, eps);
+  else if (out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, x,
+               x_stride, w, rows, d, eps);
+  else
+    return ayk_fail("ayk_rmsnorm: unknown dtype %d", out_dtype);
+  return ayk_check_launch("ayk_rmsnorm");
+}
+
+// out[t] = h_t + conv(h)_t with h = rmsnorm(x) * w, taps_w [d, taps]; state [slots, taps - 1, d]
+// float32.  max_q_len == 1 lets the kernel shift the state itself; else a second kernel does.
+AYK_EXPORT int ayk_rmsnorm_conv(void* out, const float* x, const float* w, const float* taps_w, float* state,
+                                const int* row_req, const int* req_q_start, const int* req_slot, int T, int R, int d,
+                                int taps, float eps, int max_q_len, int out_dtype, int* launched, cudaStream_t stream) {
+  if (launched) *launched = 0;
+  if (T == 0) return 0;
+  AYK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "ayk_rmsnorm_conv: %d taps, the kernel holds up to %d", taps, MAX_TAPS);
+  const int inline_state = max_q_len == 1 ? 1 : 0;
+  if (out_dtype == AYK_DTYPE_F32)
+    ayk_launch(rmsnorm_conv_kernel<float>, dim3(T), dim3(THREADS), 0, stream, (float*)out, x, w, taps_w, state, row_req,
+               req_q_start, req_slot, d, taps, eps, inline_state);
+  else if (out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(rmsnorm_conv_kernel<__nv_bfloat16>, dim3(T), dim3(THREADS), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
+               state, row_req, req_q_start, req_slot, d, taps, eps, inline_state);
+  else
+    return ayk_fail("ayk_rmsnorm_conv: unknown dtype %d", out_dtype);
+  if (launched) *launched = 1;
+  if (ayk_check_launch("ayk_rmsnorm_conv") != 0) return -1;
+  if (!inline_state && taps > 1) {
+    ayk_launch(conv_state_kernel, dim3(R), dim3(THREADS), 0, stream, state, x, w, req_q_start, req_slot, d, taps, eps);
+    if (launched) *launched = 2;
+    return ayk_check_launch("ayk_rmsnorm_conv (state)");
+  }
+  return 0;
+}
+
+AYK_EXPORT int ayk_rmsnorm_residual(float* x, const float* y, const float* w, int T, int d, float eps, float mult,
+                                    cudaStream_t stream) {
+  if (T == 0) return 0;
+  ayk_launch(rmsnorm_residual_kernel, dim3(T), dim3(THREADS), 0, stream, x, y, w, d, eps, mult);
+  return ayk_check_launch("ayk_rmsnorm_residual");
+}
+
+AYK_EXPORT int ayk_polynorm(void* out, const void* z, const float* coeff, int T, int n, float eps, int in_dtype,
+                            int out_dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32)
+    ayk_launch(polynorm_kernel<float, float>, dim3(T), dim3(THREADS), 0, stream, (float*)out, (const float*)z, coeff, n, eps);
+  else if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(polynorm_kernel<float, __nv_bfloat16>, dim3(T), dim3(THREADS), 0, stream, (__nv_bfloat16*)out,
+               (const float*)z, coeff, n, eps);
+  else if (in_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(polynorm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(THREADS), 0, stream, (__nv_bfloat16*)out,
+               (const __nv_bfloat16*)z, coeff, n, eps);
+  else
+    return ayk_fail("ayk_polynorm: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+  return ayk_check_launch("ayk_polynorm");
+}
+
+// out[t, :] = table[tok[t], :] * scale as float32.
+AYK_EXPORT int ayk_embed_scaled(float* out, const int* tok, const void* table, int T, int d, float scale, int dtype,
+                                cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int threads = d >= 256 ? 256 : 128;
+  if (dtype == AYK_DTYPE_F32)
+    ayk_launch(embed_scaled_kernel<float>, dim3(T), dim3(threads), 0, stream, out, tok, (const float*)table, d, scale);
+  else if (dtype == AYK_DTYPE_BF16)
+    ayk_launch(embed_scaled_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, tok, (const __nv_bfloat16*)table, d, scale);
+  else
+    return ayk_fail("ayk_embed_scaled: unknown dtype %d", dtype);
+  return ayk_check_launch("ayk_embed_scaled");
+}

@@ -27,11 +27,15 @@ from .scheduler import ScheduledStep, Scheduler
 from .step import StepEntry, StepRunner
 
 
+UNBOUNDED_MODEL_LEN = 8192      # positions per request for a model without a limit of its own, unless max_model_len says
+
+
 class Engine:
     def __init__(self, model, config: EngineConfig, eos_token_id: int | None = None):
         self.model = model
         self.config = config
-        self.max_model_len = min(config.max_model_len or model.max_positions, model.max_positions)
+        limit = model.max_positions or config.max_model_len or UNBOUNDED_MODEL_LEN
+        self.max_model_len = min(config.max_model_len or limit, limit)
         pages = config.kv_pages
         if config.kv_cache_bytes is not None:
             pages = pages_for_budget(model.groups, config.kv_cache_bytes, page_size=config.page_size,

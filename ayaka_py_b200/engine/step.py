@@ -155,7 +155,7 @@ class StepRunner:
             if wrong.any():
                 i = int(np.flatnonzero(wrong)[0])
                 raise ValueError(f"slot {int(live[i])}: entry starts at {int(starts[i])}, the cache holds {int(self.cache.length[live[i]])}")
-        limit = self.model.max_positions
+        limit = self.model.max_positions or self.cache.max_len
         if int(ends.max()) > limit:
             raise ValueError(f"a request would reach {int(ends.max())} tokens, the model has {limit} positions")
 

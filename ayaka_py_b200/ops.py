@@ -276,6 +276,187 @@ def ban_tokens(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) -
                                ctypes.c_int(rows.numel()), ctypes.c_int(S), ctypes.c_int(V), _stream()))
 
 
+# ------------------------------------------ rms norms, convolution, recurrences --
+
+def _f32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.float32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous float32 tensor")
+    return t
+
+
+def embed_scaled(tokens: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+    """out[t] = table[tokens[t]] * scale, float32 [T, d]."""
+    lib = _ready()
+    T, d = tokens.numel(), table.shape[1]
+    if not table.is_contiguous():
+        raise KernelError("embedding tables must be contiguous")
+    out = torch.empty((T, d), dtype=torch.float32, device=table.device)
+    _launch(lib.ayk_embed_scaled(_ptr(out), _ptr(_i32(tokens, "tokens")), _ptr(table), ctypes.c_int(T), ctypes.c_int(d),
+                                 ctypes.c_float(scale), ctypes.c_int(_tag(table.dtype)), _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dtype: torch.dtype,
+            rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight over the last axis of float32 rows (of ``x[rows]`` when rows
+    is given).  ``x`` may be a column slice of a wider matrix; statistics and weight in 32-bit."""
+    lib = _ready()
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("rmsnorm input must be float32 rows with unit column stride")
+    d = x.shape[1]
+    n = x.shape[0] if rows is None else rows.numel()
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != d or not weight.is_contiguous()):
+        raise KernelError("rmsnorm weight must be float32 of the row width")
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    elif out.dtype != out_dtype or out.shape != (n, d) or out.stride(1) != 1:
+        raise KernelError("rmsnorm: out must be [rows, width] of the output dtype")
+    _launch(lib.ayk_rmsnorm(_ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(x), ctypes.c_longlong(x.stride(0)),
+                            _ptr(weight), _ptr(None if rows is None else _i32(rows, "rows")), ctypes.c_int(n),
+                            ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def rmsnorm_conv(x: torch.Tensor, weight: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, ctx, eps: float,
+                 out_dtype: torch.dtype) -> torch.Tensor:
+    """h + conv(h) with h = rmsnorm(x) * weight: a causal convolution over time on every channel,
+    ``taps`` [width, n] float32 (tap j multiplies the input n - 1 - j steps back).  The last n - 1
+    inputs h of every request live in ``state`` [slots, n - 1, width] float32 and are brought up to
+    date.  Rows, requests and slots come from the step context."""
+    lib = _ready()
+    T, d = x.shape
+    n = taps.shape[1]
+    _f32(x, "x"); _f32(weight, "weight"); _f32(taps, "taps"); _f32(state, "state")
+    if taps.shape[0] != d or state.shape[1:] != (n - 1, d):
+        raise KernelError("rmsnorm_conv: taps [width, n] and state [slots, n - 1, width] must fit the rows")
+    out = torch.empty((T, d), dtype=out_dtype, device=x.device)
+    launched = ctypes.c_int(0)
+    code = lib.ayk_rmsnorm_conv(_ptr(out), _ptr(x), _ptr(weight), _ptr(taps), _ptr(state), _ptr(ctx.row_req),
+                                _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(T), ctypes.c_int(ctx.num_requests),
+                                ctypes.c_int(d), ctypes.c_int(n), ctypes.c_float(eps), ctypes.c_int(ctx.max_q_len),
+                                ctypes.c_int(_tag(out_dtype)), ctypes.byref(launched), _stream())
+    global launches
+    launches += launched.value
+    _check(code)
+    return out
+
+
+def rmsnorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float) -> torch.Tensor:
+    """x += mult * rmsnorm(y) * weight, in place on the float32 residual stream."""
+    lib = _ready()
+    _f32(x, "x"); _f32(y, "y"); _f32(weight, "weight")
+    if x.shape != y.shape or weight.numel() != x.shape[1]:
+        raise KernelError("rmsnorm_residual: shapes do not fit")
+    _launch(lib.ayk_rmsnorm_residual(_ptr(x), _ptr(y), _ptr(weight), ctypes.c_int(x.shape[0]), ctypes.c_int(x.shape[1]),
+                                     ctypes.c_float(eps), ctypes.c_float(mult), _stream()))
+    return x
+
+
+def polynorm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """a N(z) + b N(z^2) + c N(z^3) + e per row, N the division by the row's root mean square;
+    ``coeff`` = (a, b, c, e) float32 on the device."""
+    lib = _ready()
+    if not z.is_contiguous() or z.dim() != 2:
+        raise KernelError("polynorm: z must be contiguous rows")
+    _f32(coeff, "coeff")
+    out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    _launch(lib.ayk_polynorm(_ptr(out), _ptr(z), _ptr(coeff), ctypes.c_int(z.shape[0]), ctypes.c_int(z.shape[1]),
+                             ctypes.c_float(eps), ctypes.c_int(_tag(z.dtype)), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def rotary(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, gain: float, heads: int, head_stride: int,
+           offset: int, dims: int) -> None:
+    """Turns x[t, head * head_stride + offset + (0 .. dims)) in place: neighbouring pairs (2i, 2i+1)
+    by the angle positions[t] * freq[i], cos and sin times ``gain``.  x: rows with unit column stride."""
+    lib = _ready()
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("rotary: x must be rows with unit column stride")
+    _f32(freq, "freq")
+    if freq.numel() * 2 != dims or (heads - 1) * head_stride + offset + dims > x.shape[1]:
+        raise KernelError("rotary: heads, offset and dims do not fit the rows")
+    _launch(lib.ayk_rotary(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(_i32(positions, "positions")), _ptr(freq),
+                           ctypes.c_float(gain), ctypes.c_int(x.shape[0]), ctypes.c_int(heads), ctypes.c_int(head_stride),
+                           ctypes.c_int(offset), ctypes.c_int(dims), ctypes.c_int(_tag(x.dtype)), _stream()))
+
+
+def latent_prepare(proj: torch.Tensor, latent_pages: torch.Tensor, rope_pages: torch.Tensor, norm_weight: torch.Tensor,
+                   freq: torch.Tensor, gain: float, rot_dims: int, ctx, table: torch.Tensor, heads: int, dim: int,
+                   rot: int, rank: int, eps: float, writes: bool) -> torch.Tensor:
+    """From the float32 projection rows [q (heads x (dim + rot)) | down (rank + rot) | ...]: the normed
+    latent and the rotated shared key part go into their pages (unless ``writes`` is False), the
+    rotated query parts into the returned float32 query [T, heads, rank + rot] (columns rank ..);
+    its first rank columns per head are left for the per-head product."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(norm_weight, "norm_weight"); _f32(freq, "freq")
+    T = proj.shape[0]
+    P = latent_pages.shape[1]
+    if proj.shape[1] < heads * (dim + rot) + rank + rot or latent_pages.dtype != rope_pages.dtype:
+        raise KernelError("latent_prepare: projection rows or pages do not fit")
+    query = torch.empty((T, heads, rank + rot), dtype=torch.float32, device=proj.device)
+    _launch(lib.ayk_latent_prepare(_ptr(latent_pages), _ptr(rope_pages), _ptr(query), _ptr(proj), ctypes.c_int(proj.stride(0)),
+                                   _ptr(norm_weight), _ptr(freq), ctypes.c_float(gain), ctypes.c_int(rot_dims),
+                                   _ptr(ctx.row_req), _ptr(ctx.positions), _ptr(_i32(table, "table")),
+                                   ctypes.c_int(table.stride(0)), ctypes.c_int(P), ctypes.c_int(T), ctypes.c_int(heads),
+                                   ctypes.c_int(dim), ctypes.c_int(rot), ctypes.c_int(rank), ctypes.c_float(eps),
+                                   ctypes.c_int(1 if writes else 0), ctypes.c_int(_tag(latent_pages.dtype)), _stream()))
+    return query
+
+
+def head_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h, :] = w[h] @ a[t, h, :] (times sigmoid(gate[t, h])): a [T, H, K] float32 view (any row
+    and head stride, unit stride along K), w [H, N, K] contiguous, out [T, H, N] view, gate [T, H] view."""
+    lib = _ready()
+    T, H, K = a.shape
+    N = w.shape[1]
+    if a.dtype != torch.float32 or a.stride(2) != 1 or w.shape != (H, N, K) or not w.is_contiguous():
+        raise KernelError("head_matmul: a must be float32 [T, H, K], w [H, N, K]")
+    if out.shape != (T, H, N) or out.stride(2) != 1:
+        raise KernelError("head_matmul: out must be [T, H, N]")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (T, H) or gate.stride(1) != 1):
+        raise KernelError("head_matmul: gate must be float32 [T, H]")
+    _launch(lib.ayk_head_matmul(_ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_int(out.stride(1)), _ptr(a),
+                                ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), _ptr(gate),
+                                ctypes.c_longlong(gate.stride(0) if gate is not None else 0), ctypes.c_int(T),
+                                ctypes.c_int(H), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_tag(w.dtype)),
+                                ctypes.c_int(_tag(out.dtype)), _stream()))
+    return out
+
+
+def latent_attention(query: torch.Tensor, latent_pages: torch.Tensor, rope_pages: torch.Tensor, table: torch.Tensor,
+                     ctx, scale: float) -> torch.Tensor:
+    """Causal attention of the step's rows over cached (latent, rotated key part) pairs shared by
+    all heads: query [T, H, rank + rot] float32; returns sum_j p_j latent_j as float32 [T, H, rank]."""
+    lib = _ready()
+    T, H, Dk = query.shape
+    rank, rot = latent_pages.shape[-1], rope_pages.shape[-1]
+    if query.dtype != torch.float32 or not query.is_contiguous() or Dk != rank + rot:
+        raise KernelError("latent_attention: query must be contiguous float32 [T, H, rank + rot]")
+    out = torch.empty((T, H, rank), dtype=torch.float32, device=query.device)
+    _launch(lib.ayk_latent_attention(_ptr(out), _ptr(query), _ptr(latent_pages), _ptr(rope_pages), _ptr(_i32(table, "table")),
+                                     ctypes.c_int(table.stride(0)), _ptr(ctx.req_q_start), _ptr(ctx.req_pos0),
+                                     ctypes.c_int(ctx.num_requests), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(rank),
+                                     ctypes.c_int(rot), ctypes.c_int(latent_pages.shape[1]), ctypes.c_float(scale),
+                                     ctypes.c_int(_tag(latent_pages.dtype)), _stream()))
+    return out
+
+
+def hgrn2(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, ctx, heads: int, dim: int,
+          vdim: int) -> torch.Tensor:
+    """The HGRN2 recurrence over the step's rows, request by request, from and into ``state``
+    [slots, heads, dim, vdim] float32.  proj: float32 rows [z_q | z_f | v]; returns o [T, heads * vdim] float32."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(state, "state"); _f32(f_bias, "f_bias"); _f32(lower, "lower")
+    T = proj.shape[0]
+    if proj.shape[1] < heads * (2 * dim + vdim) or state.shape[1:] != (heads, dim, vdim):
+        raise KernelError("hgrn2: projection rows or state do not fit")
+    out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+    _launch(lib.ayk_hgrn2(_ptr(out), _ptr(state), _ptr(proj), ctypes.c_int(proj.stride(0)), _ptr(f_bias), _ptr(lower),
+                          _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(ctx.num_requests), ctypes.c_int(heads),
+                          ctypes.c_int(dim), ctypes.c_int(vdim), _stream()))
+    return out
+
+
 # ------------------------------------------------------------- dispatchers --
 
 _tc_scratch: dict = {}

@@ -277,7 +277,7 @@ class RunStep:
 class ModelSpec:
     vocab_size: int
     hidden_size: int
-    max_positions: int
+    max_positions: int | None          # None: the model itself sets no limit (the engine's max_model_len does)
     embedding: PartSpec
     position: PartSpec
     layers: tuple[LayerSpec, ...]

@@ -27,4 +27,31 @@ class PreNormBlock(Block):
         return x
 
 
+class SandwichBlock(Block):
+    """Norm before and after each sublayer, a short convolution over time in front of each:
+    x += norm1b(mixer(conv1(norm1(x)))); x += norm2b(ffn(conv2(norm2(x)))).  The closing norms carry
+    the residual multiplier and add to the stream themselves (``RMSNorm.add_normed``); the norm
+    in front and the convolution are one kernel (``TimeConv.forward``)."""
+
+    KIND = "sandwich"
+    PARTS = ("norm1", "conv1", "mixer", "norm1b", "norm2", "conv2", "ffn", "norm2b")
+
+    def forward(self, x, ctx, caches):
+        h = self.conv1.forward(x, self.norm1, ctx, caches["conv1"])
+        x = self.norm1b.add_normed(x, self.mixer.forward(h, None, ctx, caches.get("mixer")))
+        if "ffn" in self.parts:
+            h = self.conv2.forward(x, self.norm2, ctx, caches["conv2"])
+            x = self.norm2b.add_normed(x, self.ffn.forward(h, None, ctx))
+        return x
+
+
+class SandwichMixerBlock(SandwichBlock):
+    """The same without a feed-forward."""
+
+    KIND = "sandwich_mixer_only"
+    PARTS = ("norm1", "conv1", "mixer", "norm1b")
+
+
 register_block(PreNormBlock.KIND, PreNormBlock)
+register_block(SandwichBlock.KIND, SandwichBlock)
+register_block(SandwichMixerBlock.KIND, SandwichMixerBlock)

@@ -41,4 +41,29 @@ class MLP(FeedForward):
         return out
 
 
+class PolyNormMLP(FeedForward):
+    """down(act(up h)) without biases, act = PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e with powers
+    taken element by element and N the division of a token's vector by its root mean square
+    (eps inside the root); the four numbers are a tensor of the part.  The up projection is
+    stored in 32-bit, the norms are 32-bit, the activation is stored in the compute dtype."""
+
+    KIND = "polynorm_mlp"
+
+    def __init__(self, width: int, inner: int, eps: float, dtype=torch.float32, device="cuda"):
+        self.width, self.inner, self.eps, self.dtype = width, inner, float(eps), dtype
+        self.up_weight = self.down_weight = self.coeff = None
+
+    def tensors(self):
+        return {"up_weight": TensorDecl((self.inner, self.width), "matrix"),
+                "down_weight": TensorDecl((self.width, self.inner), "matrix"),
+                "coeff": TensorDecl((4,), "vector")}
+
+    def forward(self, h, residual, ctx):
+        """residual + ff(h); with ``residual`` None the sublayer's output alone, float32."""
+        z = ops.linear(h, self.up_weight, None, out_dtype=torch.float32)
+        u = ops.polynorm(z, self.coeff, self.eps, self.dtype)
+        return ops.linear(u, self.down_weight, None, residual=residual, out_dtype=torch.float32, out=residual)
+
+
 register_part(MLP.KIND, MLP)
+register_part(PolyNormMLP.KIND, PolyNormMLP)

@@ -1,4 +1,4 @@
-"""LayerNorm: statistics and affine in 32-bit (``layers/norm.py:198-205``)."""
+"""LayerNorm and RMS norm: statistics and affine in 32-bit (``layers/norm.py:198-205``)."""
 
 from __future__ import annotations
 
@@ -30,4 +30,30 @@ class LayerNorm(Norm):
         return builder.layernorm(x, self.weight, self.bias, self.eps, self.width, self.dtype, wanted=wanted)
 
 
+class RMSNorm(Norm):
+    """x / sqrt(mean(x^2) + eps) * weight, eps inside the root, all in 32-bit.  ``out_scale`` is a
+    constant factor on the result: a norm that closes a sublayer carries the residual multiplier
+    there, and ``add_normed`` adds its scaled output to the residual stream in one kernel."""
+
+    KIND = "rmsnorm"
+
+    def __init__(self, width: int, eps: float, out_scale: float = 1.0, dtype=torch.float32, device="cuda"):
+        self.width, self.eps, self.out_scale = width, float(eps), float(out_scale)
+        self.dtype = dtype
+        self.weight = None
+
+    def tensors(self):
+        return {"weight": TensorDecl((self.width,), "vector")}
+
+    def forward(self, x, ctx, rows=None):
+        if self.out_scale != 1.0:
+            raise ValueError("an RMS norm with an output factor only adds to the residual stream (add_normed)")
+        return ops.rmsnorm(x, self.weight, self.eps, self.dtype, rows=rows)
+
+    def add_normed(self, x, y):
+        """x += out_scale * norm(y), in place; x and y float32 [T, width]."""
+        return ops.rmsnorm_residual(x, y, self.weight, self.eps, self.out_scale)
+
+
 register_part(LayerNorm.KIND, LayerNorm)
+register_part(RMSNorm.KIND, RMSNorm)

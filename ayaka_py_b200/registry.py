@@ -37,8 +37,11 @@ def registered_architectures() -> list[str]:
 
 
 def architecture_for(document: dict) -> Architecture:
-    """Chosen by ``architectures[0]``; by ``model_type`` if that key is absent."""
+    """Chosen by ``architectures[0]`` (or the single name under ``architecture``); by ``model_type``
+    if neither key is there."""
     names = document.get("architectures") or []
+    if not names and isinstance(document.get("architecture"), str):
+        names = [document["architecture"]]
     if names:
         if names[0] in _ARCHITECTURES:
             return _ARCHITECTURES[names[0]]

@@ -45,11 +45,13 @@ class ReplaySession:
         ops.library()
         self.config, self.model = load_model(model_dir, dtype, device)
         pages = -(-max_tokens // page_size) + 1                # + the padding page
+        # no request can hold more than the pool; a model without a position limit gets that one
+        longest = -(-max_tokens // page_size) * page_size
+        max_len = min(self.model.max_positions or longest, longest)
         self.cache = CacheManager(self.model.groups, kv_pages=pages, page_size=page_size,
-                                  max_requests=max_requests, max_len=self.model.max_positions,
+                                  max_requests=max_requests, max_len=max_len,
                                   dtype=self.model.dtype, device=device)
-        self.runner = StepRunner(self.model, self.cache,
-                                 max_tokens=min(max_tokens, 4 * self.model.max_positions))
+        self.runner = StepRunner(self.model, self.cache, max_tokens=min(max_tokens, 4 * max_len))
         self.slots: dict[str, int] = {}
 
     def step(self, record: dict):
