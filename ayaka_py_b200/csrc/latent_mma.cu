@@ -1,0 +1,350 @@
+// Latent attention on the tensor cores (bfloat16 operands, 32-bit scores, weights and sums).
+//
+// The same arithmetic as latent.cu: a head's query is [U_k^T q_n ; q_r] (rank + rot numbers), a key
+// is the cached pair [c ; k_r], the weighted sum runs over c.  All heads share the keys, so a block
+// takes 16 x WM (row, head) pairs of one request -- BR consecutive rows times HG heads -- against one
+// tile of 32 cached positions at a time:
+//   S = Q K^T      mma.sync m16n8k16, Q [pairs, rank + rot] and the key tile in shared memory
+//   online softmax in registers (exp2, running maximum and sum per pair)
+//   O += P C       the key tile's first rank columns are the values
+// A warp owns 16 pairs and RPW columns of O (accumulators in registers); when the latent is wider
+// than RPW, CG warps share the pairs, each computing S again for its columns.  With one row per
+// request (decoding) a block has WM = 1 and the context is cut into partitions of PART positions
+// (grid.z) whose partial results (maximum, sum, unnormalised O) a second kernel merges.
+//
+// tcgen05 is not used here: O for 128 pairs x 512 columns would fill tensor memory alone, and
+// the score tile's K extent (rank + rot up to 576) wants operands staged in more shared memory
+// than one SM has beside it; the warp-level form keeps O in registers and works for every latent
+// size that is a multiple of 8.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int NK = 32;          // cached positions per tile
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async_16(void* smem_ptr, const void* gmem_ptr) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem_ptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// partial: [pairs of the step = T * H][parts][2 + rank] floats (maximum in the log2 domain, sum, O).
+template <int RPW, int CG, int WM>
+__global__ void __launch_bounds__(32 * WM * CG)
+latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial, const float* __restrict__ query,
+                            const __nv_bfloat16* __restrict__ latent_pages, const __nv_bfloat16* __restrict__ rope_pages,
+                            const int* __restrict__ table, int table_stride, const int* __restrict__ req_q_start,
+                            const int* __restrict__ req_pos0, int num_req, int H, int HG, int BR, int rank, int rot,
+                            int page_size, float scale_log2, int parts, int part_keys) {
+  constexpr int AQ = 16 * WM;
+  pdl_trigger();
+  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
+  for (int r = 0; r < num_req; ++r) {
+    const int len = req_q_start[r + 1] - req_q_start[r];
+    const int tiles = (len + BR - 1) / BR;
+    if (tile < tiles) { req = r; q0 = tile * BR; q_len = len; break; }
+    tile -= tiles;
+  }
+  if (req < 0) return;
+  const int h0 = blockIdx.y * HG;
+  const int heads = min(HG, H - h0);
+  const int rows = min(BR, q_len - q0);
+  const int row0 = req_q_start[req] + q0;
+  const int pos0 = req_pos0[req] + q0;
+  const int last_pos = pos0 + rows - 1;
+  const int part = blockIdx.z;
+  const int key_lo = part * part_keys;
+  const int key_hi = parts > 1 ? min(last_pos, key_lo + part_keys - 1) : last_pos;      // inclusive
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = warp % WM, cg = warp / WM;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int Dk = rank + rot;
+  const int Dp = (Dk + 15) & ~15;
+  const int ld = Dp + 8;                     // bf16 elements per row of the tiles: rows shift by 16 bytes
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [AQ][ld]
+  __nv_bfloat16* Ks = Qs + AQ * ld;                                    // two buffers of [NK][ld]
+  const int* my_table = table + (size_t)req * table_stride;
+
+  pdl_wait();
+  if (parts > 1 && key_lo > key_hi) {        // a partition beyond the context: nothing seen
+    for (int pr = threadIdx.x; pr < AQ; pr += blockDim.x) {
+      const int r = pr / HG, hh = pr - r * HG;
+      if (r < rows && hh < heads && pr < BR * HG) {
+        float* dst = partial + (((size_t)(row0 + r) * H + h0 + hh) * parts + part) * (size_t)(rank + 2);
+        dst[0] = -INFINITY;
+        dst[1] = 0.f;
+      }
+    }
+    return;
+  }
+  // the pairs' queries as bfloat16
+  for (int i = threadIdx.x; i < AQ * (Dp / 2); i += blockDim.x) {
+    const int pr = i / (Dp / 2), d = (i - pr * (Dp / 2)) * 2;
+    const int r = pr / HG, hh = pr - r * HG;
+    float a = 0.f, b = 0.f;
+    if (r < rows && hh < heads && pr < BR * HG) {
+      const float* q = query + ((size_t)(row0 + r) * H + h0 + hh) * Dk;
+      if (d < Dk) a = q[d];
+      if (d + 1 < Dk) b = q[d + 1];
+    }
+    *reinterpret_cast<uint32_t*>(Qs + pr * ld + d) = pack_bf16(a, b);
+  }
+
+  // this thread's two pairs: rows g and g + 8 of the warp's 16
+  int qpos[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int pr = wm * 16 + g + 8 * e;
+    const int r = pr / HG, hh = pr - r * HG;
+    qpos[e] = (r < rows && hh < heads && pr < BR * HG) ? pos0 + r : -1;
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[RPW / 8][4];
+#pragma unroll
+  for (int j = 0; j < RPW / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  const int col0 = cg * RPW;                 // first column of O that this warp owns
+
+  // A tile of 32 cached positions: a warp copies whole rows (16-byte pieces, asynchronously); rows that
+  // are not there (beyond the range, the padding page) and the padding columns are zeros.  Two
+  // buffers: tile i + 1 is on its way while tile i is used.
+  const int chunks_lat = rank / 8, chunks_rot = rot / 8, chunks = Dp / 8;
+  const int nwarps = WM * CG;
+  auto fetch = [&](int k0, __nv_bfloat16* dst) {
+    for (int j = warp; j < NK; j += nwarps) {
+      const int kp = k0 + j;
+      int page = 0;
+      if (kp <= key_hi) page = my_table[kp / page_size];
+      const size_t at = (size_t)page * page_size + (kp % page_size);
+      for (int c = lane; c < chunks; c += 32) {
+        __nv_bfloat16* to = dst + j * ld + c * 8;
+        if (page > 0 && c < chunks_lat) cp_async_16(to, latent_pages + at * rank + c * 8);
+        else if (page > 0 && c < chunks_lat + chunks_rot) cp_async_16(to, rope_pages + at * rot + (c - chunks_lat) * 8);
+        else *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    cp_async_commit();
+  };
+  __nv_bfloat16* Kbuf[2] = {Ks, Ks + NK * ld};
+  if (key_lo <= key_hi) fetch(key_lo, Kbuf[0]);
+  int it = 0;
+  for (int k0 = key_lo; k0 <= key_hi; k0 += NK, ++it) {
+    const bool more = k0 + NK <= key_hi;
+    if (more) fetch(k0 + NK, Kbuf[(it + 1) & 1]);
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    const __nv_bfloat16* Kt = Kbuf[it & 1];
+
+    // S = Q K^T for the warp's 16 pairs and the tile's 32 positions
+    float s[NK / 8][4];
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll 4
+    for (int ks = 0; ks < Dp; ks += 16) {
+      uint32_t a[4];
+      ldmatrix_x4(a, Qs + (wm * 16 + (lane & 15)) * ld + ks + (lane >> 4) * 8);
+#pragma unroll
+      for (int jp = 0; jp < NK / 16; ++jp) {
+        uint32_t b[4];
+        ldmatrix_x4(b, Kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + ks + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * jp], a, b[0], b[1]);
+        mma_bf16(s[2 * jp + 1], a, b[2], b[3]);
+      }
+    }
+    // scale, mask, running maximum
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kp = k0 + j * 8 + 2 * t4 + (e & 1);
+        const int which = e >> 1;
+        const bool valid = kp <= qpos[which] && kp <= key_hi && my_table[kp / page_size] > 0;
+        s[j][e] = valid ? s[j][e] * scale_log2 : -INFINITY;
+        m_new[which] = fmaxf(m_new[which], s[j][e]);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 1));
+      m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 2));
+      m_use[e] = m_new[e] == -INFINITY ? 0.f : m_new[e];
+      alpha[e] = exp2f(m_run[e] - m_use[e]);        // exp2(-inf) = 0 before the first visible key
+      m_run[e] = m_new[e];
+      l_run[e] *= alpha[e];
+    }
+    uint32_t p[NK / 16][4];
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) {
+      const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+      const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      p[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+      p[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int j = 0; j < RPW / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
+    // O += P C over the warp's columns
+#pragma unroll
+    for (int kk = 0; kk < NK / 16; ++kk) {
+#pragma unroll
+      for (int jp = 0; jp < RPW / 16; ++jp) {
+        const int d0 = col0 + jp * 16;
+        if (d0 < rank) {                       // warp-uniform
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, Kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + d0 + (lane >> 4) * 8);
+          mma_bf16(o[2 * jp], p[kk], b[0], b[1]);
+          mma_bf16(o[2 * jp + 1], p[kk], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();        // the buffer is free for the tile after the next
+  }
+
+  // the sums of a pair are spread over the four threads of its quad
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
+  }
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    if (qpos[e] < 0) continue;
+    const int pr = wm * 16 + g + 8 * e;
+    const int r = pr / HG, hh = pr - r * HG;
+    const size_t pair = (size_t)(row0 + r) * H + h0 + hh;
+    if (parts > 1) {
+      float* dst = partial + (pair * parts + part) * (size_t)(rank + 2);
+      if (cg == 0 && t4 == 0) { dst[0] = m_run[e]; dst[1] = l_run[e]; }
+#pragma unroll
+      for (int j = 0; j < RPW / 8; ++j) {
+        const int d = col0 + j * 8 + 2 * t4;
+        if (d < rank) { dst[2 + d] = o[j][2 * e]; dst[2 + d + 1] = o[j][2 * e + 1]; }
+      }
+    } else {
+      const float inv = l_run[e] > 0.f ? 1.f / l_run[e] : 0.f;
+      float* dst = out + pair * rank;
+#pragma unroll
+      for (int j = 0; j < RPW / 8; ++j) {
+        const int d = col0 + j * 8 + 2 * t4;
+        if (d < rank) *reinterpret_cast<float2*>(dst + d) = make_float2(o[j][2 * e] * inv, o[j][2 * e + 1] * inv);
+      }
+    }
+  }
+}
+
+// out[pair, :] = sum_p exp2(m_p - m) O_p / sum_p exp2(m_p - m) l_p, partitions in order.
+__global__ void latent_merge_kernel(float* __restrict__ out, const float* __restrict__ partial, int rank, int parts) {
+  pdl_trigger();
+  pdl_wait();
+  const float* src = partial + (size_t)blockIdx.x * parts * (rank + 2);
+  float m = -INFINITY;
+  for (int p = 0; p < parts; ++p) m = fmaxf(m, src[(size_t)p * (rank + 2)]);
+  float l = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    const float mp = src[(size_t)p * (rank + 2)];
+    if (mp > -INFINITY) l += exp2f(mp - m) * src[(size_t)p * (rank + 2) + 1];
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float acc = 0.f;
+    for (int p = 0; p < parts; ++p) {
+      const float mp = src[(size_t)p * (rank + 2)];
+      if (mp > -INFINITY) acc = fmaf(exp2f(mp - m), src[(size_t)p * (rank + 2) + 2 + d], acc);
+    }
+    out[(size_t)blockIdx.x * rank + d] = acc * inv;
+  }
+}
+
+template <int RPW, int CG, int WM>
+int launch(float* out, float* partial, const float* query, const void* latent_pages, const void* rope_pages, const int* table,
+           int table_stride, const int* req_q_start, const int* req_pos0, int num_req, int total_rows, int H, int rank, int rot,
+           int page_size, float scale, int parts, int part_keys, cudaStream_t stream) {
+  constexpr int AQ = 16 * WM;
+  const int HG = H < AQ ? H : AQ;
+  const int BR = AQ / HG;
+  const int Dp = (rank + rot + 15) & ~15;
+  const size_t smem = (size_t)(AQ + 2 * NK) * (Dp + 8) * sizeof(__nv_bfloat16);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t err = cudaFuncSetAttribute(latent_attention_mma_kernel<RPW, CG, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return ayk_fail("ayk_latent_attention_mma: shared memory %zu: %s", smem, cudaGetErrorString(err));
+    configured = smem;
+  }
+  dim3 grid(total_rows / BR + num_req, (H + HG - 1) / HG, parts);
+  ayk_launch(latent_attention_mma_kernel<RPW, CG, WM>, grid, dim3(32 * WM * CG), smem, stream, out, partial, query,
+             (const __nv_bfloat16*)latent_pages, (const __nv_bfloat16*)rope_pages, table, table_stride, req_q_start, req_pos0,
+             num_req, H, HG, BR, rank, rot, page_size, scale * 1.4426950408889634f, parts, part_keys);
+  return ayk_check_launch("ayk_latent_attention_mma");
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes these sizes: 16-byte pieces of the cached rows, O within the registers.
+AYK_EXPORT int ayk_latent_attention_mma_takes(int rank, int rot) {
+  return rank >= 8 && rank % 8 == 0 && rot % 8 == 0 && rank <= 512 && rank + rot <= 1024;
+}
+
+// As ayk_latent_attention, bfloat16 pages.  parts > 1 (only with one row per request): the context
+// is cut into partitions of part_keys positions; partial holds T * H * parts * (rank + 2) floats.
+AYK_EXPORT int ayk_latent_attention_mma(float* out, float* partial, const float* query, const void* latent_pages,
+                                        const void* rope_pages, const int* table, int table_stride, const int* req_q_start,
+                                        const int* req_pos0, int num_req, int total_rows, int max_q_len, int H, int rank,
+                                        int rot, int page_size, float scale, int parts, int part_keys, int* launched,
+                                        cudaStream_t stream) {
+  if (launched) *launched = 0;
+  if (num_req == 0 || total_rows == 0) return 0;
+  AYK_REQUIRE(ayk_latent_attention_mma_takes(rank, rot), "ayk_latent_attention_mma: latent %d + %d is not taken", rank, rot);
+  AYK_REQUIRE(parts == 1 || max_q_len == 1, "ayk_latent_attention_mma: the context is cut only for single rows");
+  AYK_REQUIRE(parts >= 1 && parts <= 65535 && (parts == 1 || part_keys % NK == 0), "ayk_latent_attention_mma: %d partitions of %d", parts, part_keys);
+  const bool single = max_q_len == 1 && H <= 16;
+  int rc;
+#define AYK_LM(RPW, CG)                                                                                                     \
+  rc = single ? launch<RPW, CG, 1>(out, partial, query, latent_pages, rope_pages, table, table_stride, req_q_start, req_pos0, \
+                                   num_req, total_rows, H, rank, rot, page_size, scale, parts, part_keys, stream)             \
+              : launch<RPW, CG, 4>(out, partial, query, latent_pages, rope_pages, table, table_stride, req_q_start, req_pos0, \
+                                   num_req, total_rows, H, rank, rot, page_size, scale, parts, part_keys, stream)
+  if (rank <= 64) { AYK_LM(64, 1); }
+  else if (rank <= 128) { AYK_LM(128, 1); }
+  else if (rank <= 256) { AYK_LM(256, 1); }
+  else { AYK_LM(256, 2); }
+#undef AYK_LM
+  if (rc != 0) return rc;
+  if (launched) *launched = 1;
+  if (parts > 1) {
+    ayk_launch(latent_merge_kernel, dim3(total_rows * H), dim3(rank >= 256 ? 128 : 64), 0, stream, out, (const float*)partial, rank, parts);
+    if (launched) *launched = 2;
+    return ayk_check_launch("ayk_latent_attention_mma (merge)");
+  }
+  return 0;
+}

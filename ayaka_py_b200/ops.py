@@ -423,16 +423,45 @@ def head_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch
     return out
 
 
+LATENT_PARTS = 64        # at most this many partitions of the context when every request brings one row
+
+
 def latent_attention(query: torch.Tensor, latent_pages: torch.Tensor, rope_pages: torch.Tensor, table: torch.Tensor,
-                     ctx, scale: float) -> torch.Tensor:
+                     ctx, scale: float, tensor_cores: bool | None = None) -> torch.Tensor:
     """Causal attention of the step's rows over cached (latent, rotated key part) pairs shared by
-    all heads: query [T, H, rank + rot] float32; returns sum_j p_j latent_j as float32 [T, H, rank]."""
+    all heads: query [T, H, rank + rot] float32; returns sum_j p_j latent_j as float32 [T, H, rank].
+    bfloat16 pages whose rows are whole 16-byte pieces go through the tensor-core kernel (a decode
+    step's context cut into partitions and merged); 32-bit pages and other sizes through the
+    kernel on the FP32 pipes."""
     lib = _ready()
     T, H, Dk = query.shape
     rank, rot = latent_pages.shape[-1], rope_pages.shape[-1]
     if query.dtype != torch.float32 or not query.is_contiguous() or Dk != rank + rot:
         raise KernelError("latent_attention: query must be contiguous float32 [T, H, rank + rot]")
     out = torch.empty((T, H, rank), dtype=torch.float32, device=query.device)
+    takes = latent_pages.dtype == torch.bfloat16 and bool(lib.ayk_latent_attention_mma_takes(ctypes.c_int(rank), ctypes.c_int(rot)))
+    if tensor_cores is None:
+        tensor_cores = takes
+    elif tensor_cores and not takes:
+        raise KernelError(f"latent_attention: the tensor-core kernel does not take {latent_pages.dtype} pages of {rank} + {rot}")
+    if tensor_cores:
+        parts, part_keys, partial = 1, 0, None
+        if ctx.max_q_len == 1:
+            part_keys = max(64, -(-(-(-ctx.cache.max_len // LATENT_PARTS)) // 32) * 32)
+            parts = -(-ctx.cache.max_len // part_keys)
+            if parts > 1:
+                partial = torch.empty((T * H * parts * (rank + 2),), dtype=torch.float32, device=query.device)
+        launched = ctypes.c_int(0)
+        code = lib.ayk_latent_attention_mma(_ptr(out), _ptr(partial), _ptr(query), _ptr(latent_pages), _ptr(rope_pages),
+                                            _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)), _ptr(ctx.req_q_start),
+                                            _ptr(ctx.req_pos0), ctypes.c_int(ctx.num_requests), ctypes.c_int(T),
+                                            ctypes.c_int(ctx.max_q_len), ctypes.c_int(H), ctypes.c_int(rank), ctypes.c_int(rot),
+                                            ctypes.c_int(latent_pages.shape[1]), ctypes.c_float(scale), ctypes.c_int(parts),
+                                            ctypes.c_int(part_keys), ctypes.byref(launched), _stream())
+        global launches
+        launches += launched.value
+        _check(code)
+        return out
     _launch(lib.ayk_latent_attention(_ptr(out), _ptr(query), _ptr(latent_pages), _ptr(rope_pages), _ptr(_i32(table, "table")),
                                      ctypes.c_int(table.stride(0)), _ptr(ctx.req_q_start), _ptr(ctx.req_pos0),
                                      ctypes.c_int(ctx.num_requests), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(rank),

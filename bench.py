@@ -31,7 +31,11 @@ prompts and step counts and prints the same line with ``"impl": "reference"``.
 ``--only prefill|small|large|products`` runs one workload alone (for profiling):
 ``products`` prints, a JSON line each, the four matrix products of an XL layer
 through the engine's dispatcher over row counts beside ``torch.matmul`` on the same
-operands.
+operands.  ``--only rakalix`` measures the Rakalix design (latent attention and HGRN2
+layers in turn, PolyNorm feed-forward) beside GPT-2 at equal width, depth and inner
+width: a 2,048-token prefill step, decode steps of ``--batch`` requests, and each
+kernel of the design beside the like kernel of GPT-2 against its roofline; a JSON
+line per width.
 """
 
 from __future__ import annotations
@@ -412,6 +416,214 @@ def run_large_mixed(layers: int | None = None, steps: int = 48, warmup: int = 6,
             "mean_context": mean_ctx, "n_layer": L}
 
 
+def rakalix_document(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Rakalix model of real-layer sizes: heads of 128, a latent of 512 + 64 rotated, inner width 2.75 x."""
+    heads, ff = width // 128, width * 11 // 4
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+              "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                        "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    recurrent = {"type": "hgrn2", "mlp": {"kind": "dense", "ff": ff}, "mixer": {"heads": heads, "dim": 128, "vdim": 128}}
+    return {"architecture": "Rakalix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+            "layers": [recurrent if i % 2 == 0 else latent for i in range(layers)]}
+
+
+def run_rakalix(width: int, layers: int, batch: int, steps: int, warmup: int, pk: dict) -> dict:
+    """Rakalix beside GPT-2 at equal width, depth and inner width (bfloat16, random weights): prefill of
+    2 x 1,024 tokens in one step, decode of ``batch`` requests after 512-token prompts through the engine
+    (CUDA graphs), and the design's kernels one by one.  Every kernel is timed alone with CUDA events
+    as a CUDA graph replayed after the L2 was overwritten (256 MB written), median of 9."""
+    import numpy as np
+    import torch
+
+    from ayaka_py_b200 import EngineConfig, GPT2Config, Request, SamplingParams, StopCriteria, ops
+    from ayaka_py_b200.config.model import RakalixConfig
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import random_model
+    from ayaka_py_b200.engine.step import StepEntry
+
+    vocab, ff, heads = 32000, width * 11 // 4, width // 128
+    configs = {"rakalix": RakalixConfig.from_dict(rakalix_document(width, layers, vocab)),
+               "gpt2": GPT2Config(n_layer=layers, n_embd=width, n_head=width // 64, n_inner=ff, vocab_size=vocab,
+                                  n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")}
+    flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    rs = np.random.RandomState(3)
+
+    def timed(fn, reps=9):
+        """Median device time of fn's kernels: captured once in a CUDA graph (no interpreter time
+        between the events), replayed after the L2 was overwritten."""
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        out = []
+        for _ in range(reps):
+            flush.fill_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return sorted(out)[len(out) // 2]
+
+    result = {"width": width, "layers": layers, "inner": ff, "batch": batch}
+    kernels = []
+
+    def kernel(name, model, ms, gbytes=None, gflop=None, like=None):
+        row = {"kernel": name, "model": model, "us": round(ms * 1e3, 1)}
+        if gbytes is not None:
+            row.update(gb_s=round(gbytes / (ms / 1e3), 1), frac=round(gbytes / (ms / 1e3) / pk["hbm_gbs"], 4), bound="hbm")
+        if gflop is not None:
+            row.update(tflops=round(gflop / ms, 2), frac=round(gflop / ms / pk["bf16_tflops"], 4), bound="bf16")
+        if like:
+            row["like"] = like
+        kernels.append(row)
+
+    for name, config in configs.items():
+        model = random_model(config, 1, "bfloat16", "cuda", generate_on_device=True)
+        engine = Engine(model, EngineConfig(dtype="bfloat16", kv_pages=batch * 64 + 130, page_size=16, max_requests=max(batch, 2),
+                                            batch_tokens=2048, prefill_chunk=2048, max_model_len=1024, decode_graph=True),
+                        eos_token_id=None)
+        cache, runner = engine.cache, engine.runner
+
+        # ---- prefill: 2 x 1,024 tokens in one step
+        def prefill_step():
+            slots = [cache.open(f"p{i}") for i in range(2)]
+            entries = [StepEntry(sl, 0, rs.randint(0, vocab, 1024).tolist(), [1023]) for sl in slots]
+            res = cache.reserve([(e.slot, 0, 1024) for e in entries])
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            runner.run(entries)
+            b.record()
+            torch.cuda.synchronize()
+            cache.commit(res)
+            for sl in slots:
+                cache.close(sl)
+            return a.elapsed_time(b)
+        times = [prefill_step() for _ in range(5)][2:]
+        prefill_ms = sorted(times)[1]
+
+        # ---- decode through the engine's own loop
+        total_new = 2 * warmup + steps + 8
+        for i in range(batch):
+            engine.submit(Request(f"d{i}", rs.randint(0, vocab, PROMPT_LEN).tolist(), SamplingParams(temperature=0.0),
+                                  StopCriteria(max_tokens=total_new, ignore_eos=True)))
+        while any(st.computed < st.prompt_len for st in engine.scheduler.states.values()):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        a.record()
+        for _ in range(steps):
+            engine.step()
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        decode_ms = a.elapsed_time(b) / steps
+        weights = model.weight_bytes()
+        result[name] = {"prefill_tok_s": round(2048 / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                        "decode_tok_s": round(batch / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                        "decode_e2e_tok_s": round(batch * steps / wall, 1), "weight_gb": round(weights / 1e9, 3),
+                        "decode_hbm_frac": round(weights / (decode_ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                        "kv_bytes_per_token": cache.bytes_per_token()}
+        for rid in list(engine.scheduler.states):
+            engine.abort(rid)
+        engine.finished.clear()
+
+        # ---- kernels alone, on the shapes of the two steps above
+        d, T = width, 2048
+        bf, f32 = torch.bfloat16, torch.float32
+        x = torch.randn(T, d, device="cuda")
+        pairs = 2 * (1024 * 1025 // 2)                 # (query, key) pairs of two causal prompts of 1,024
+        ctx_len = PROMPT_LEN + 64
+
+        def open_step(lengths, starts=None):
+            slots = [cache.open(f"k{i}") for i in range(len(lengths))]
+            if starts:
+                res = cache.reserve([(sl, 0, st) for sl, st in zip(slots, starts)])
+                cache.commit(res)
+            res = cache.reserve([(sl, int(cache.length[sl]), n) for sl, n in zip(slots, lengths)])
+            ctx = runner.prepare([StepEntry(sl, int(cache.length[sl]), [0] * n, []) for sl, n in zip(slots, lengths)])
+            return ctx, res, slots
+
+        def close_step(res, slots):
+            cache.rollback(res)
+            for sl in slots:
+                cache.close(sl)
+
+        for label, lengths, starts in (("prefill", [1024, 1024], None), ("decode", [1] * batch, [ctx_len] * batch)):
+            ctx, res, slots = open_step(lengths, starts)
+            rows = ctx.num_rows
+            xr = x[:rows].contiguous()
+            if name == "gpt2":
+                block = model.blocks[0]
+                ms = timed(lambda: ops.layernorm(xr, block.norm1.weight, block.norm1.bias, 1e-5, bf))
+                kernel(f"layernorm ({label})", name, ms, gbytes=rows * d * 6 / 1e9)
+                att = block.mixer
+                kc, vc = cache.kv_layer(0, 0)
+                qkv = torch.randn(rows, 3 * d, device="cuda").to(bf)
+                ms = timed(lambda: ops.attention(qkv[:, :d], kc, vc, ctx.tables[0], ctx, att.num_heads, att.scale, None,
+                                                 append=(qkv[:, d:2 * d], qkv[:, 2 * d:])))
+                if label == "prefill":
+                    kernel("attention_tc + kv_append (prefill)", name, ms, gflop=pairs * att.num_heads * 4 * 64 / 1e9)
+                else:
+                    kernel("attention_decode + merge", name, ms, gbytes=batch * (ctx_len + 1) * 2 * d * 2 / 1e9)
+                ms = timed(lambda: ops.linear(xr.to(bf), block.ffn.up_weight, block.ffn.up_bias, activation="gelu_tanh", out_dtype=bf))
+                kernel(f"linear {rows}x{ff}x{d} + gelu ({label})", name, ms, gflop=2.0 * rows * ff * d / 1e9)
+            else:
+                rec, lat = model.blocks[0], model.blocks[1]
+                bind = {n: b for n, b in zip(("rec", "lat"), (model.bindings[0], model.bindings[1]))}
+                ms = timed(lambda: rec.conv1.forward(xr, rec.norm1, ctx, bind["rec"]["conv1"]))
+                kernel(f"rmsnorm + time conv ({label})", name, ms, gbytes=rows * d * 6 / 1e9, like="layernorm")
+                y = torch.randn(rows, d, device="cuda")
+                ms = timed(lambda: rec.norm1b.add_normed(xr, y))
+                kernel(f"rmsnorm + residual ({label})", name, ms, gbytes=rows * d * 12 / 1e9, like="layernorm")
+                z = torch.randn(rows, ff, device="cuda")
+                ms = timed(lambda: ops.polynorm(z, rec.ffn.coeff, 1e-6, bf))
+                kernel(f"polynorm ({label})", name, ms, gbytes=rows * ff * 6 / 1e9, like="layernorm")
+                ms = timed(lambda: ops.linear(xr.to(bf), rec.ffn.up_weight, None, out_dtype=f32))
+                kernel(f"linear {rows}x{ff}x{d}, 32-bit out ({label})", name, ms, gflop=2.0 * rows * ff * d / 1e9, like="linear + gelu")
+                # HGRN2 recurrence
+                mx = rec.mixer
+                proj = torch.randn(rows, mx.in_weight.shape[0], device="cuda")
+                state = cache.state_layer(bind["rec"]["mixer"].group, bind["rec"]["mixer"].layer)
+                ms = timed(lambda: ops.hgrn2(proj, state, mx.f_bias, mx.lower, ctx, heads, 128, 128))
+                if label == "prefill":
+                    kernel("hgrn2 recurrence (prefill)", name, ms, gflop=4.0 * rows * heads * 128 * 128 / 1e9, like="attention_tc")
+                else:
+                    kernel("hgrn2 recurrence (decode)", name, ms, gbytes=batch * heads * 128 * 128 * 8 / 1e9, like="attention_decode")
+                # latent attention and the products around it
+                la = lat.mixer
+                rope_pages, latent_pages = cache.kv_layer(bind["lat"]["mixer"].group, bind["lat"]["mixer"].layer)
+                table = ctx.tables[bind["lat"]["mixer"].group]
+                proj = torch.randn(rows, la.in_weight.shape[0], device="cuda")
+                ms = timed(lambda: ops.latent_prepare(proj, latent_pages, rope_pages, la.down_norm, la.rotary.freq, la.rotary.gain,
+                                                      la.rotary.dims, ctx, table, heads, 128, 64, 512, 1e-6, True))
+                kernel(f"latent prepare ({label})", name, ms, gbytes=rows * (la.in_weight.shape[0] * 4 + 576 * 2 + heads * 64 * 4) / 1e9,
+                       like="kv_append")
+                query = torch.randn(rows, heads, 576, device="cuda")
+                qv = proj[:, :la.q_width].view(rows, heads, 192)[:, :, :128]
+                ms = timed(lambda: ops.head_matmul(qv, la.uk_heads, query[:, :, :512]))
+                kernel(f"per-head product K128 N512 ({label})", name, ms, gflop=2.0 * rows * heads * 128 * 512 / 1e9, like="linear")
+                ms = timed(lambda: ops.latent_attention(query, latent_pages, rope_pages, table, ctx, la.scale))
+                if label == "prefill":
+                    kernel("latent attention (prefill)", name, ms, gflop=pairs * heads * 2 * (576 + 512) / 1e9, like="attention_tc")
+                else:
+                    kernel("latent attention + merge (decode)", name, ms, gbytes=batch * (ctx_len + 1) * 576 * 2 / 1e9, like="attention_decode")
+            close_step(res, slots)
+        del engine, model
+        torch.cuda.empty_cache()
+    result["kernels"] = kernels
+    result["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    return result
+
+
 def reference_line(args) -> dict:
     """The reference arm: same shape, batch, prompt length and step counts, the reference's own engine."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -461,7 +673,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-graph", action="store_true", help="run decode steps eagerly")
     parser.add_argument("--no-points", action="store_true", help="only the decode steps at --batch")
-    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products"),
+    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix: the model widths to measure")
+    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix"),
                         help="run one workload alone and print its numbers (for profiling): the 2,048-token prefill "
                              "step, the small shape's continuous batching, the large shape's mixed steps, or the four "
                              "products of an XL layer over row counts beside the library's matmul")
@@ -484,6 +697,11 @@ def main() -> int:
 
     pk = peaks()
     graph = not args.no_graph
+    if args.only == "rakalix":
+        for width in (int(w) for w in args.widths.split(",")):
+            layers = 4 if args.layers == XL["n_layer"] else args.layers
+            print(json.dumps({"rakalix_beside_gpt2": run_rakalix(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
+        return 0
     if args.only == "products":
         for row in run_products():
             print(json.dumps(row))
