@@ -1,4 +1,5 @@
-// Latent attention on the tensor cores (bfloat16 operands, 32-bit scores, weights and sums).
+// Latent attention on the tensor cores (bfloat16 operands, 32-bit scores, weights and sums), and the
+// small per-head matrix products in front of and behind it.
 //
 // The same arithmetic as latent.cu: a head's query is [U_k^T q_n ; q_r] (rank + rot numbers), a key
 // is the cached pair [c ; k_r], the weighted sum runs over c.  All heads share the keys, so a block
@@ -103,17 +104,20 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
     }
     return;
   }
-  // the pairs' queries as bfloat16
-  for (int i = threadIdx.x; i < AQ * (Dp / 2); i += blockDim.x) {
-    const int pr = i / (Dp / 2), d = (i - pr * (Dp / 2)) * 2;
+  // the pairs' queries as bfloat16 (rank and rot are multiples of 8, so a pair's row is whole float4s;
+  // the padding columns are zeros)
+  const int quads = Dp / 4;
+#pragma unroll 4
+  for (int i = threadIdx.x; i < AQ * quads; i += blockDim.x) {
+    const int pr = i / quads, d = (i - pr * quads) * 4;
     const int r = pr / HG, hh = pr - r * HG;
-    float a = 0.f, b = 0.f;
-    if (r < rows && hh < heads && pr < BR * HG) {
-      const float* q = query + ((size_t)(row0 + r) * H + h0 + hh) * Dk;
-      if (d < Dk) a = q[d];
-      if (d + 1 < Dk) b = q[d + 1];
-    }
-    *reinterpret_cast<uint32_t*>(Qs + pr * ld + d) = pack_bf16(a, b);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows && hh < heads && pr < BR * HG && d < Dk)
+      v = *reinterpret_cast<const float4*>(query + ((size_t)(row0 + r) * H + h0 + hh) * Dk + d);
+    uint2 packed;
+    packed.x = pack_bf16(v.x, v.y);
+    packed.y = pack_bf16(v.z, v.w);
+    *reinterpret_cast<uint2*>(Qs + pr * ld + d) = packed;
   }
 
   // this thread's two pairs: rows g and g + 8 of the warp's 16
@@ -286,6 +290,82 @@ __global__ void latent_merge_kernel(float* __restrict__ out, const float* __rest
   }
 }
 
+// ------------------------------------------------------- per-head products --
+// out[t, h, n] = (sum_k a[t, h, k] w[h, n, k]) (* sigmoid(gate[t, h])) with bfloat16 weights on the
+// tensor cores: a block takes 64 rows x 64 columns of one head, K in chunks of 64.  The float32
+// operand goes into shared memory as two bfloat16 parts (its rounding and what the rounding left
+// over), each multiplied with the weights, so that it keeps 16 bits of mantissa; sums are 32-bit.
+constexpr int PM = 64, PN = 64, PK = 64, PLD = PK + 8;
+
+template <typename O>
+__global__ void __launch_bounds__(128)
+head_matmul_mma_kernel(O* __restrict__ out, long long out_row, int out_head, const float* __restrict__ a, long long a_row,
+                       int a_head, const __nv_bfloat16* __restrict__ w, const float* __restrict__ gate, long long gate_row,
+                       int T, int N, int K) {
+  __shared__ __align__(16) __nv_bfloat16 As[PM * PLD];
+  __shared__ __align__(16) __nv_bfloat16 Al[PM * PLD];       // what rounding to bfloat16 left over
+  __shared__ __align__(16) __nv_bfloat16 Ws[PN * PLD];
+  pdl_trigger();
+  const int h = blockIdx.y, t0 = blockIdx.x * PM, n0 = blockIdx.z * PN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  float acc[PN / 8][4];
+#pragma unroll
+  for (int j = 0; j < PN / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  pdl_wait();
+  for (int k0 = 0; k0 < K; k0 += PK) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < PM * (PK / 4); i += 128) {        // four floats of a at a time
+      const int r = i / (PK / 4), c = (i - r * (PK / 4)) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t0 + r < T && k0 + c < K) v = *reinterpret_cast<const float4*>(a + (size_t)(t0 + r) * a_row + (size_t)h * a_head + k0 + c);
+      const __nv_bfloat162 h01 = __floats2bfloat162_rn(v.x, v.y), h23 = __floats2bfloat162_rn(v.z, v.w);
+      uint2 hi, lo;
+      hi.x = *reinterpret_cast<const uint32_t*>(&h01);
+      hi.y = *reinterpret_cast<const uint32_t*>(&h23);
+      lo.x = pack_bf16(v.x - __bfloat162float(h01.x), v.y - __bfloat162float(h01.y));
+      lo.y = pack_bf16(v.z - __bfloat162float(h23.x), v.w - __bfloat162float(h23.y));
+      *reinterpret_cast<uint2*>(As + r * PLD + c) = hi;
+      *reinterpret_cast<uint2*>(Al + r * PLD + c) = lo;
+    }
+    for (int i = threadIdx.x; i < PN * (PK / 8); i += 128) {        // eight weights at a time
+      const int r = i / (PK / 8), c = (i - r * (PK / 8)) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (n0 + r < N && k0 + c < K) v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + r) * K + k0 + c);
+      *reinterpret_cast<uint4*>(Ws + r * PLD + c) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < PK; ks += 16) {
+      uint32_t af[4], al[4];
+      ldmatrix_x4(af, As + (warp * 16 + (lane & 15)) * PLD + ks + (lane >> 4) * 8);
+      ldmatrix_x4(al, Al + (warp * 16 + (lane & 15)) * PLD + ks + (lane >> 4) * 8);
+#pragma unroll
+      for (int jp = 0; jp < PN / 16; ++jp) {
+        uint32_t b[4];
+        ldmatrix_x4(b, Ws + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * PLD + ks + ((lane >> 3) & 1) * 8);
+        mma_bf16(acc[2 * jp], al, b[0], b[1]);
+        mma_bf16(acc[2 * jp + 1], al, b[2], b[3]);
+        mma_bf16(acc[2 * jp], af, b[0], b[1]);
+        mma_bf16(acc[2 * jp + 1], af, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int t = t0 + warp * 16 + g + 8 * e;
+    if (t >= T) continue;
+    const float scale = gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + h])) : 1.0f;
+    O* dst = out + (size_t)t * out_row + (size_t)h * out_head;
+#pragma unroll
+    for (int j = 0; j < PN / 8; ++j) {
+      const int n = n0 + j * 8 + 2 * t4;
+      if (n < N) dst[n] = from_float<O>(acc[j][2 * e] * scale);
+      if (n + 1 < N) dst[n + 1] = from_float<O>(acc[j][2 * e + 1] * scale);
+    }
+  }
+}
+
 template <int RPW, int CG, int WM>
 int launch(float* out, float* partial, const float* query, const void* latent_pages, const void* rope_pages, const int* table,
            int table_stride, const int* req_q_start, const int* req_pos0, int num_req, int total_rows, int H, int rank, int rot,
@@ -347,4 +427,28 @@ AYK_EXPORT int ayk_latent_attention_mma(float* out, float* partial, const float*
     return ayk_check_launch("ayk_latent_attention_mma (merge)");
   }
   return 0;
+}
+
+// As ayk_head_matmul for bfloat16 weights, on the tensor cores.  K a multiple of 8, the float32
+// operand's rows and heads on 16-byte boundaries (the caller checks with ayk_head_matmul_mma_takes).
+AYK_EXPORT int ayk_head_matmul_mma_takes(const void* a, long long a_row, int a_head, int K) {
+  return K % 8 == 0 && a_row % 4 == 0 && a_head % 4 == 0 && (uintptr_t)a % 16 == 0;
+}
+
+AYK_EXPORT int ayk_head_matmul_mma(void* out, long long out_row, int out_head, const float* a, long long a_row, int a_head,
+                                   const void* w, const float* gate, long long gate_row, int T, int H, int N, int K,
+                                   int out_dtype, cudaStream_t stream) {
+  if (T == 0 || H == 0 || N == 0) return 0;
+  AYK_REQUIRE(ayk_head_matmul_mma_takes(a, a_row, a_head, K), "ayk_head_matmul_mma: operand layout is not taken (K %d)", K);
+  dim3 grid((T + PM - 1) / PM, H, (N + PN - 1) / PN);
+  AYK_REQUIRE(H <= 65535 && grid.z <= 65535, "ayk_head_matmul_mma: too many heads or columns");
+  if (out_dtype == AYK_DTYPE_F32)
+    ayk_launch(head_matmul_mma_kernel<float>, grid, dim3(128), 0, stream, (float*)out, out_row, out_head, a, a_row, a_head,
+               (const __nv_bfloat16*)w, gate, gate_row, T, N, K);
+  else if (out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(head_matmul_mma_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (__nv_bfloat16*)out, out_row, out_head, a,
+               a_row, a_head, (const __nv_bfloat16*)w, gate, gate_row, T, N, K);
+  else
+    return ayk_fail("ayk_head_matmul_mma: unknown dtype %d", out_dtype);
+  return ayk_check_launch("ayk_head_matmul_mma");
 }

@@ -36,6 +36,26 @@ __device__ __forceinline__ void block_sums_128(float (&v)[N], float* red) {
   for (int i = 0; i < N; ++i) v[i] = (red[i * 4] + red[i * 4 + 1]) + (red[i * 4 + 2] + red[i * 4 + 3]);
 }
 
+// The same for a block of any number of whole warps (red: N x 32 floats).
+template <int N>
+__device__ __forceinline__ void block_sums_any(float (&v)[N], float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = warp_sum(v[i]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) red[i * 32 + warp] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    float total = 0.f;
+    for (int w = 0; w < nwarp; ++w) total += red[i * 32 + w];      // the same order in every thread
+    v[i] = total;
+  }
+}
+
 // ----------------------------------------------------------------- rmsnorm --
 // out[r, :] = x[src(r), :d] / rms * w.  One block per row.
 template <typename O>
@@ -68,12 +88,12 @@ rmsnorm_kernel(O* __restrict__ out, long long out_stride, const float* __restric
 constexpr int MAX_TAPS = 8;
 
 template <typename O>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(1024)
 rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                     const float* __restrict__ taps_w, float* __restrict__ state, const int* __restrict__ row_req,
                     const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps,
                     int inline_state) {
-  __shared__ float red[4 * MAX_TAPS];
+  __shared__ float red[32 * MAX_TAPS];
   pdl_trigger();
   const int t = blockIdx.x;
   const int req = row_req[t];
@@ -85,7 +105,7 @@ rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const floa
   float sums[MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < MAX_TAPS; ++j) sums[j] = 0.f;
-  for (int i = threadIdx.x; i < d; i += THREADS) {
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
 #pragma unroll
     for (int j = 0; j < MAX_TAPS; ++j) {
       const int s = t - j;                       // j rows back
@@ -95,12 +115,12 @@ rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const floa
       }
     }
   }
-  block_sums_128<MAX_TAPS>(sums, red);
+  block_sums_any<MAX_TAPS>(sums, red);
   float inv[MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < MAX_TAPS; ++j) inv[j] = 1.0f / sqrtf(sums[j] / (float)d + eps);
   float* st = state + (size_t)slot * back * d;
-  for (int i = threadIdx.x; i < d; i += THREADS) {
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float wi = w[i];
     const float h0 = x[(size_t)t * d + i] * inv[0] * wi;
     float acc = h0 * (1.0f + taps_w[(size_t)i * taps + back]);
@@ -257,11 +277,15 @@ AYK_EXPORT int ayk_rmsnorm_conv(void* out, const float* x, const float* w, const
   if (T == 0) return 0;
   AYK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "ayk_rmsnorm_conv: %d taps, the kernel holds up to %d", taps, MAX_TAPS);
   const int inline_state = max_q_len == 1 ? 1 : 0;
+  // few rows (a decode step): many threads per row, so that a row's loads are in flight together
+  int threads = THREADS;
+  if (T <= 256) threads = min(1024, max(THREADS, (d / 2 + 31) / 32 * 32));
+  else if (d >= 2048) threads = 256;
   if (out_dtype == AYK_DTYPE_F32)
-    ayk_launch(rmsnorm_conv_kernel<float>, dim3(T), dim3(THREADS), 0, stream, (float*)out, x, w, taps_w, state, row_req,
+    ayk_launch(rmsnorm_conv_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)out, x, w, taps_w, state, row_req,
                req_q_start, req_slot, d, taps, eps, inline_state);
   else if (out_dtype == AYK_DTYPE_BF16)
-    ayk_launch(rmsnorm_conv_kernel<__nv_bfloat16>, dim3(T), dim3(THREADS), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
+    ayk_launch(rmsnorm_conv_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
                state, row_req, req_q_start, req_slot, d, taps, eps, inline_state);
   else
     return ayk_fail("ayk_rmsnorm_conv: unknown dtype %d", out_dtype);

@@ -415,11 +415,16 @@ def head_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch
         raise KernelError("head_matmul: out must be [T, H, N]")
     if gate is not None and (gate.dtype != torch.float32 or gate.shape != (T, H) or gate.stride(1) != 1):
         raise KernelError("head_matmul: gate must be float32 [T, H]")
-    _launch(lib.ayk_head_matmul(_ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_int(out.stride(1)), _ptr(a),
-                                ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), _ptr(gate),
-                                ctypes.c_longlong(gate.stride(0) if gate is not None else 0), ctypes.c_int(T),
-                                ctypes.c_int(H), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_tag(w.dtype)),
-                                ctypes.c_int(_tag(out.dtype)), _stream()))
+    common = (_ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_int(out.stride(1)), _ptr(a),
+              ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), _ptr(gate),
+              ctypes.c_longlong(gate.stride(0) if gate is not None else 0), ctypes.c_int(T), ctypes.c_int(H),
+              ctypes.c_int(N), ctypes.c_int(K))
+    # bfloat16 weights: the tensor cores, the float32 operand rounded on its way in; else the FP32 pipes
+    if w.dtype == torch.bfloat16 and lib.ayk_head_matmul_mma_takes(_ptr(a), ctypes.c_longlong(a.stride(0)),
+                                                                   ctypes.c_int(a.stride(1)), ctypes.c_int(K)):
+        _launch(lib.ayk_head_matmul_mma(*common, ctypes.c_int(_tag(out.dtype)), _stream()))
+    else:
+        _launch(lib.ayk_head_matmul(*common, ctypes.c_int(_tag(w.dtype)), ctypes.c_int(_tag(out.dtype)), _stream()))
     return out
 
 
@@ -447,7 +452,7 @@ def latent_attention(query: torch.Tensor, latent_pages: torch.Tensor, rope_pages
     if tensor_cores:
         parts, part_keys, partial = 1, 0, None
         if ctx.max_q_len == 1:
-            part_keys = max(64, -(-(-(-ctx.cache.max_len // LATENT_PARTS)) // 32) * 32)
+            part_keys = max(32, -(-(-(-ctx.cache.max_len // LATENT_PARTS)) // 32) * 32)
             parts = -(-ctx.cache.max_len // part_keys)
             if parts > 1:
                 partial = torch.empty((T * H * parts * (rank + 2),), dtype=torch.float32, device=query.device)
@@ -471,18 +476,29 @@ def latent_attention(query: torch.Tensor, latent_pages: torch.Tensor, rope_pages
 
 
 def hgrn2(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, ctx, heads: int, dim: int,
-          vdim: int) -> torch.Tensor:
+          vdim: int, chunked: bool | None = None) -> torch.Tensor:
     """The HGRN2 recurrence over the step's rows, request by request, from and into ``state``
-    [slots, heads, dim, vdim] float32.  proj: float32 rows [z_q | z_f | v]; returns o [T, heads * vdim] float32."""
+    [slots, heads, dim, vdim] float32.  proj: float32 rows [z_q | z_f | v]; returns o [T, heads * vdim] float32.
+    ``chunked``: the kernel that takes 16 tokens at a time (default: whenever a request brings more than one row)."""
     lib = _ready()
     _f32(proj, "proj"); _f32(state, "state"); _f32(f_bias, "f_bias"); _f32(lower, "lower")
     T = proj.shape[0]
     if proj.shape[1] < heads * (2 * dim + vdim) or state.shape[1:] != (heads, dim, vdim):
         raise KernelError("hgrn2: projection rows or state do not fit")
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+    if chunked is None:
+        chunked = ctx.max_q_len > 1
+    scratch = None
+    if chunked:
+        lib.ayk_hgrn2_scratch_floats.restype = ctypes.c_longlong
+        floats = int(lib.ayk_hgrn2_scratch_floats(ctypes.c_int(T), ctypes.c_int(ctx.num_requests), ctypes.c_int(heads), ctypes.c_int(dim)))
+        scratch = torch.empty((floats,), dtype=torch.float32, device=proj.device)
     _launch(lib.ayk_hgrn2(_ptr(out), _ptr(state), _ptr(proj), ctypes.c_int(proj.stride(0)), _ptr(f_bias), _ptr(lower),
-                          _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(ctx.num_requests), ctypes.c_int(heads),
-                          ctypes.c_int(dim), ctypes.c_int(vdim), _stream()))
+                          _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(ctx.num_requests), ctypes.c_int(T),
+                          ctypes.c_int(heads), ctypes.c_int(dim), ctypes.c_int(vdim), _ptr(scratch), _stream()))
+    if chunked:
+        global launches
+        launches += 1
     return out
 
 
