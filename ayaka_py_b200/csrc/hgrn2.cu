@@ -118,7 +118,7 @@ int launch(float* out, float* state, const float* proj, int proj_stride, const f
 // K' = k e^(b_last - b), the chunk's decay e^(b_last) and the 16 x 16 matrix A, into scratch.
 // hgrn2_chunk_scan: one block per (request, head, 32 value columns) walks the request's chunks in
 // order, the state in registers: o = Q'^T S + A v, then S = diag(e^(b_last)) S + K' v^T.
-constexpr int CT = 16;
+constexpr int CT = 16, SW = 8;      // tokens per chunk; warps of the walk over chunks (each holds an eighth of the state's rows)
 
 // floats of scratch per (chunk, head): Q' and K' [dim][CT], the decay [dim rounded up to 4], A [CT][CT]; a multiple of 4
 __host__ __device__ inline size_t chunk_floats(int dim) { return (size_t)2 * CT * dim + ((dim + 3) & ~3) + CT * CT; }
@@ -203,19 +203,23 @@ __device__ __forceinline__ void cp_async_16(void* smem_ptr, const void* gmem_ptr
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem_ptr) : "memory");
 }
+__device__ __forceinline__ void cp_async_4(void* smem_ptr, const void* gmem_ptr) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(addr), "l"(gmem_ptr) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int DP>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(SW * 32)
 hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, const float* __restrict__ scratch,
                         const float* __restrict__ proj, int proj_stride, const int* __restrict__ req_q_start,
                         const int* __restrict__ req_slot, int H, int dim, int vdim) {
   extern __shared__ __align__(16) float smem[];
   const size_t per_chunk = chunk_floats(dim);              // a multiple of 4 floats
   float* stage[2] = {smem, smem + per_chunk + CT * COLS};  // per buffer: the chunk's scratch, then v [CT][COLS]
-  float* red = smem + 2 * (per_chunk + CT * COLS);         // [WARPS][CT][COLS]
+  float* red = smem + 2 * (per_chunk + CT * COLS);         // [SW][CT][COLS]
   pdl_trigger();
   const int req = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
   const int first = req_q_start[req], n = req_q_start[req + 1] - first;
@@ -225,7 +229,7 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col = c0 + lane;
   const bool col_ok = col < vdim;
-  const int per = (dim + WARPS - 1) / WARPS;
+  const int per = (dim + SW - 1) / SW;
   const int i0 = warp * per;
   const int vcol = 2 * H * dim + h * vdim;
   pdl_wait();
@@ -244,7 +248,8 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
     const int steps = min(CT, n - c * CT);
     for (int i = threadIdx.x; i < CT * COLS; i += blockDim.x) {
       const int tt = i / COLS, cc = i - tt * COLS;
-      v[i] = (tt < steps && c0 + cc < vdim) ? proj[(size_t)(first + c * CT + tt) * proj_stride + vcol + c0 + cc] : 0.f;
+      if (tt < steps && c0 + cc < vdim) cp_async_4(v + i, proj + (size_t)(first + c * CT + tt) * proj_stride + vcol + c0 + cc);
+      else v[i] = 0.f;
     }
     cp_async_commit();
   };
@@ -267,7 +272,7 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
         const float4* qf4 = reinterpret_cast<const float4*>(qfT + (size_t)(i0 + i) * CT);
         const float4* kw4 = reinterpret_cast<const float4*>(kwT + (size_t)(i0 + i) * CT);
         const float old = s[i];
-        float fresh = gs[i0 + i] * old;
+        float fresh = gs[i0 + i] * old, fresh2 = 0.f;      // two chains: the sums of a row do not wait for one another
 #pragma unroll
         for (int u = 0; u < CT / 4; ++u) {
           const float4 a = qf4[u], w = kw4[u];
@@ -276,19 +281,21 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
           acc[4 * u + 2] = fmaf(a.z, old, acc[4 * u + 2]);
           acc[4 * u + 3] = fmaf(a.w, old, acc[4 * u + 3]);
           fresh = fmaf(w.x, v[4 * u], fresh);
-          fresh = fmaf(w.y, v[4 * u + 1], fresh);
+          fresh2 = fmaf(w.y, v[4 * u + 1], fresh2);
           fresh = fmaf(w.z, v[4 * u + 2], fresh);
-          fresh = fmaf(w.w, v[4 * u + 3], fresh);
+          fresh2 = fmaf(w.w, v[4 * u + 3], fresh2);
         }
-        s[i] = fresh;
+        s[i] = fresh + fresh2;
       }
     }
 #pragma unroll
     for (int tt = 0; tt < CT; ++tt) red[(warp * CT + tt) * COLS + lane] = acc[tt];
     __syncthreads();
-    // warp w finishes tokens w, w + 4, ...: the four partial sums plus what the chunk itself wrote
-    for (int tt = warp; tt < steps; tt += WARPS) {
-      float o = (red[tt * COLS + lane] + red[(CT + tt) * COLS + lane]) + (red[(2 * CT + tt) * COLS + lane] + red[(3 * CT + tt) * COLS + lane]);
+    // warp w finishes tokens w and w + 8: the warps' partial sums (in order) plus what the chunk itself wrote
+    for (int tt = warp; tt < steps; tt += SW) {
+      float o = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < SW; ++w8) o += red[(w8 * CT + tt) * COLS + lane];
       for (int sidx = 0; sidx <= tt; ++sidx) o = fmaf(As[tt * CT + sidx], vs[sidx * COLS + lane], o);
       if (col_ok) out[(size_t)(first + c * CT + tt) * ((size_t)H * vdim) + h * vdim + col] = o;
     }
@@ -306,7 +313,7 @@ int launch_chunk(float* out, float* state, float* scratch, const float* proj, in
                  const float* lower, const int* req_q_start, const int* req_slot, int R, int T, int H, int dim, int vdim,
                  cudaStream_t stream) {
   const size_t smem_p = (size_t)3 * CT * (dim + 1) * sizeof(float);
-  const size_t smem_s = (2 * (chunk_floats(dim) + CT * COLS) + (size_t)WARPS * CT * COLS) * sizeof(float);
+  const size_t smem_s = (2 * (chunk_floats(dim) + CT * COLS) + (size_t)SW * CT * COLS) * sizeof(float);
   static size_t configured_p = 48 * 1024, configured_s = 48 * 1024;
   if (smem_p > configured_p) {
     cudaError_t err = cudaFuncSetAttribute(hgrn2_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
@@ -321,7 +328,7 @@ int launch_chunk(float* out, float* state, float* scratch, const float* proj, in
   ayk_launch(hgrn2_chunk_prepare_kernel, dim3(T / CT + R, H), dim3(128), smem_p, stream, scratch, proj, proj_stride, f_bias,
              lower, req_q_start, R, H, dim);
   if (ayk_check_launch("ayk_hgrn2 (chunk prepare)") != 0) return -1;
-  ayk_launch(hgrn2_chunk_scan_kernel<DP>, dim3((vdim + COLS - 1) / COLS, H, R), dim3(WARPS * 32), smem_s, stream, out, state,
+  ayk_launch(hgrn2_chunk_scan_kernel<DP>, dim3((vdim + COLS - 1) / COLS, H, R), dim3(SW * 32), smem_s, stream, out, state,
              (const float*)scratch, proj, proj_stride, req_q_start, req_slot, H, dim, vdim);
   return ayk_check_launch("ayk_hgrn2 (chunk scan)");
 }
@@ -340,10 +347,17 @@ AYK_EXPORT int ayk_hgrn2(float* out, float* state, const float* proj, int proj_s
   AYK_REQUIRE(dim >= 1 && dim <= 512, "ayk_hgrn2: %d channels per head, the kernel holds up to 512", dim);
   AYK_REQUIRE(H <= 65535 && R <= 65535, "ayk_hgrn2: too many heads or requests");
   const int per = (dim + WARPS - 1) / WARPS;
-#define AYK_HG(DP)                                                                                                              \
-  return scratch ? launch_chunk<DP>(out, state, scratch, proj, proj_stride, f_bias, lower, req_q_start, req_slot, R, T, H, dim, \
-                                    vdim, stream)                                                                               \
-                 : launch<DP>(out, state, proj, proj_stride, f_bias, lower, req_q_start, req_slot, R, H, dim, vdim, stream)
+  if (scratch) {
+    const int per8 = (dim + SW - 1) / SW;
+#define AYK_HC(DP) return launch_chunk<DP>(out, state, scratch, proj, proj_stride, f_bias, lower, req_q_start, req_slot, R, T, H, dim, vdim, stream)
+    if (per8 <= 4) AYK_HC(4);
+    if (per8 <= 8) AYK_HC(8);
+    if (per8 <= 16) AYK_HC(16);
+    if (per8 <= 32) AYK_HC(32);
+    AYK_HC(64);
+#undef AYK_HC
+  }
+#define AYK_HG(DP) return launch<DP>(out, state, proj, proj_stride, f_bias, lower, req_q_start, req_slot, R, H, dim, vdim, stream)
   if (per <= 8) AYK_HG(8);
   if (per <= 16) AYK_HG(16);
   if (per <= 32) AYK_HG(32);

@@ -63,7 +63,8 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
                             int page_size, float scale_log2, int parts, int part_keys) {
   constexpr int AQ = 16 * WM;
   pdl_trigger();
-  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
+  // the last tiles of a request see the most keys: they start first (blocks are handed out in order)
+  int tile = gridDim.x - 1 - blockIdx.x, req = -1, q0 = 0, q_len = 0;
   for (int r = 0; r < num_req; ++r) {
     const int len = req_q_start[r + 1] - req_q_start[r];
     const int tiles = (len + BR - 1) / BR;
@@ -90,6 +91,7 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [AQ][ld]
   __nv_bfloat16* Ks = Qs + AQ * ld;                                    // two buffers of [NK][ld]
+  int* there = reinterpret_cast<int*>(Ks + 2 * NK * ld);                // per buffer and position: is it cached (a page, inside the range)
   const int* my_table = table + (size_t)req * table_stride;
 
   pdl_wait();
@@ -139,12 +141,13 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
   // buffers: tile i + 1 is on its way while tile i is used.
   const int chunks_lat = rank / 8, chunks_rot = rot / 8, chunks = Dp / 8;
   const int nwarps = WM * CG;
-  auto fetch = [&](int k0, __nv_bfloat16* dst) {
+  auto fetch = [&](int k0, __nv_bfloat16* dst, int* flags) {
     for (int j = warp; j < NK; j += nwarps) {
       const int kp = k0 + j;
       int page = 0;
       if (kp <= key_hi) page = my_table[kp / page_size];
       const size_t at = (size_t)page * page_size + (kp % page_size);
+      if (lane == 0) flags[j] = page > 0;
       for (int c = lane; c < chunks; c += 32) {
         __nv_bfloat16* to = dst + j * ld + c * 8;
         if (page > 0 && c < chunks_lat) cp_async_16(to, latent_pages + at * rank + c * 8);
@@ -155,14 +158,15 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
     cp_async_commit();
   };
   __nv_bfloat16* Kbuf[2] = {Ks, Ks + NK * ld};
-  if (key_lo <= key_hi) fetch(key_lo, Kbuf[0]);
+  if (key_lo <= key_hi) fetch(key_lo, Kbuf[0], there);
   int it = 0;
   for (int k0 = key_lo; k0 <= key_hi; k0 += NK, ++it) {
     const bool more = k0 + NK <= key_hi;
-    if (more) fetch(k0 + NK, Kbuf[(it + 1) & 1]);
+    if (more) fetch(k0 + NK, Kbuf[(it + 1) & 1], there + ((it + 1) & 1) * NK);
     if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
     const __nv_bfloat16* Kt = Kbuf[it & 1];
+    const int* cached = there + (it & 1) * NK;
 
     // S = Q K^T for the warp's 16 pairs and the tile's 32 positions
     float s[NK / 8][4];
@@ -186,9 +190,9 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
     for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int kp = k0 + j * 8 + 2 * t4 + (e & 1);
+        const int kj = j * 8 + 2 * t4 + (e & 1);
         const int which = e >> 1;
-        const bool valid = kp <= qpos[which] && kp <= key_hi && my_table[kp / page_size] > 0;
+        const bool valid = k0 + kj <= qpos[which] && cached[kj];
         s[j][e] = valid ? s[j][e] * scale_log2 : -INFINITY;
         m_new[which] = fmaxf(m_new[which], s[j][e]);
       }
@@ -374,7 +378,7 @@ int launch(float* out, float* partial, const float* query, const void* latent_pa
   const int HG = H < AQ ? H : AQ;
   const int BR = AQ / HG;
   const int Dp = (rank + rot + 15) & ~15;
-  const size_t smem = (size_t)(AQ + 2 * NK) * (Dp + 8) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(AQ + 2 * NK) * (Dp + 8) * sizeof(__nv_bfloat16) + 2 * NK * sizeof(int);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
     cudaError_t err = cudaFuncSetAttribute(latent_attention_mma_kernel<RPW, CG, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -56,6 +56,30 @@ __device__ __forceinline__ void block_sums_any(float (&v)[N], float* red) {
   }
 }
 
+// The first n of N sums only (the rest are left as they are).
+template <int N>
+__device__ __forceinline__ void block_sums_upto(float (&v)[N], float* red, int n) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    if (i < n) v[i] = warp_sum(v[i]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (i < n) red[i * 32 + warp] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    if (i < n) {
+      float total = 0.f;
+      for (int w = 0; w < nwarp; ++w) total += red[i * 32 + w];      // the same order in every thread
+      v[i] = total;
+    }
+  }
+}
+
 // ----------------------------------------------------------------- rmsnorm --
 // out[r, :] = x[src(r), :d] / rms * w.  One block per row.
 template <typename O>
@@ -123,7 +147,7 @@ rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const floa
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float wi = w[i];
     const float h0 = x[(size_t)t * d + i] * inv[0] * wi;
-    float acc = h0 * (1.0f + taps_w[(size_t)i * taps + back]);
+    float acc = h0 * (1.0f + taps_w[(size_t)back * d + i]);
     float held[MAX_TAPS];                        // the state's values of this channel (inline update)
 #pragma unroll
     for (int j = 1; j < MAX_TAPS; ++j) {
@@ -133,7 +157,7 @@ rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const floa
         if (s >= first) hv = x[(size_t)s * d + i] * inv[j] * wi;
         else hv = st[(size_t)(back + (s - first)) * d + i];      // s - first in [-back, -1]
         held[j] = hv;
-        acc = fmaf(taps_w[(size_t)i * taps + back - j], hv, acc);
+        acc = fmaf(taps_w[(size_t)(back - j) * d + i], hv, acc);
       }
     }
     out[(size_t)t * d + i] = from_float<O>(acc);
@@ -147,12 +171,100 @@ rmsnorm_conv_kernel(O* __restrict__ out, const float* __restrict__ x, const floa
   }
 }
 
+// The same for rows of whole float4s up to 4,096 wide: a thread keeps its (up to two) float4 columns
+// of the row and of the earlier rows in registers between the two passes, so every row is read once
+// per block, 16 bytes at a time.
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 w;
+  w.x = *reinterpret_cast<uint32_t*>(&lo);
+  w.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+
+template <typename O>
+__global__ void __launch_bounds__(512, 2)
+rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                        const float* __restrict__ taps_w, float* __restrict__ state, const int* __restrict__ row_req,
+                        const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps,
+                        int inline_state) {
+  __shared__ float red[32 * MAX_TAPS];
+  constexpr int V = 2;
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int req = row_req[t];
+  const int first = req_q_start[req];
+  const int slot = req_slot[req];
+  const int nv = d >> 2, back = taps - 1;
+  pdl_wait();
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  float4 xv[MAX_TAPS][V];
+  float sums[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) {
+    sums[j] = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const int idx = threadIdx.x + v * blockDim.x;
+      xv[j][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j <= back && t - j >= first && idx < nv) {
+        xv[j][v] = x4[(size_t)(t - j) * nv + idx];
+        sums[j] += (xv[j][v].x * xv[j][v].x + xv[j][v].y * xv[j][v].y) + (xv[j][v].z * xv[j][v].z + xv[j][v].w * xv[j][v].w);
+      }
+    }
+  }
+  block_sums_upto<MAX_TAPS>(sums, red, taps);
+  float inv[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) inv[j] = j <= back ? 1.0f / sqrtf(sums[j] / (float)d + eps) : 0.f;
+  float4* st4 = reinterpret_cast<float4*>(state + (size_t)slot * back * d);
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int idx = threadIdx.x + v * blockDim.x;
+    if (idx >= nv) continue;
+    const float4 wi = reinterpret_cast<const float4*>(w)[idx];
+    float4 h[MAX_TAPS];
+    h[0] = make_float4(xv[0][v].x * inv[0] * wi.x, xv[0][v].y * inv[0] * wi.y, xv[0][v].z * inv[0] * wi.z, xv[0][v].w * inv[0] * wi.w);
+#pragma unroll
+    for (int j = 1; j < MAX_TAPS; ++j) {
+      if (j <= back) {
+        const int s = t - j;
+        if (s >= first) h[j] = make_float4(xv[j][v].x * inv[j] * wi.x, xv[j][v].y * inv[j] * wi.y, xv[j][v].z * inv[j] * wi.z, xv[j][v].w * inv[j] * wi.w);
+        else h[j] = st4[(size_t)(back + (s - first)) * nv + idx];
+      }
+    }
+    float acc[4];
+    const float4* tw4 = reinterpret_cast<const float4*>(taps_w);   // [taps][d]: a tap of four neighbouring channels is one float4
+    const float4 t0 = tw4[(size_t)back * nv + idx];
+    acc[0] = h[0].x * (1.0f + t0.x); acc[1] = h[0].y * (1.0f + t0.y);
+    acc[2] = h[0].z * (1.0f + t0.z); acc[3] = h[0].w * (1.0f + t0.w);
+#pragma unroll
+    for (int j = 1; j < MAX_TAPS; ++j) {
+      if (j <= back) {
+        const float4 tj = tw4[(size_t)(back - j) * nv + idx];
+        acc[0] = fmaf(tj.x, h[j].x, acc[0]); acc[1] = fmaf(tj.y, h[j].y, acc[1]);
+        acc[2] = fmaf(tj.z, h[j].z, acc[2]); acc[3] = fmaf(tj.w, h[j].w, acc[3]);
+      }
+    }
+    store4(out + (size_t)t * d + 4 * idx, acc[0], acc[1], acc[2], acc[3]);
+    if (inline_state) {
+#pragma unroll
+      for (int j = MAX_TAPS - 1; j >= 2; --j)
+        if (j <= back) st4[(size_t)(back - j) * nv + idx] = h[j - 1];
+      if (back >= 1) st4[(size_t)(back - 1) * nv + idx] = h[0];
+    }
+  }
+}
+
 // The state after a step: the last taps - 1 of (old state, the portion's inputs h).  One block
 // per request; a thread reads what it needs of its channels before it writes them.
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(1024)
 conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, const float* __restrict__ w,
                   const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps) {
-  __shared__ float red[4 * MAX_TAPS];
+  __shared__ float red[32 * MAX_TAPS];
   pdl_trigger();
   const int req = blockIdx.x;
   const int first = req_q_start[req], n = req_q_start[req + 1] - first;
@@ -162,7 +274,7 @@ conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, const 
   float sums[MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < MAX_TAPS; ++j) sums[j] = 0.f;
-  for (int i = threadIdx.x; i < d; i += THREADS) {
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
 #pragma unroll
     for (int j = 0; j < MAX_TAPS; ++j) {
       const int k = n - 1 - j;                   // j rows before the portion's end
@@ -172,9 +284,9 @@ conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, const 
       }
     }
   }
-  block_sums_128<MAX_TAPS>(sums, red);
+  block_sums_any<MAX_TAPS>(sums, red);
   float* st = state + (size_t)slot * back * d;
-  for (int i = threadIdx.x; i < d; i += THREADS) {
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float fresh[MAX_TAPS];
 #pragma unroll
     for (int j = 0; j < MAX_TAPS; ++j) {
@@ -268,7 +380,7 @@ AYK_EXPORT int ayk_rmsnorm(void* out, long long out_stride, const float* x, long
   return ayk_check_launch("ayk_rmsnorm");
 }
 
-// out[t] = h_t + conv(h)_t with h = rmsnorm(x) * w, taps_w [d, taps]; state [slots, taps - 1, d]
+// out[t] = h_t + conv(h)_t with h = rmsnorm(x) * w, taps_w [taps, d] (tap-major); state [slots, taps - 1, d]
 // float32.  max_q_len == 1 lets the kernel shift the state itself; else a second kernel does.
 AYK_EXPORT int ayk_rmsnorm_conv(void* out, const float* x, const float* w, const float* taps_w, float* state,
                                 const int* row_req, const int* req_q_start, const int* req_slot, int T, int R, int d,
@@ -277,22 +389,39 @@ AYK_EXPORT int ayk_rmsnorm_conv(void* out, const float* x, const float* w, const
   if (T == 0) return 0;
   AYK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "ayk_rmsnorm_conv: %d taps, the kernel holds up to %d", taps, MAX_TAPS);
   const int inline_state = max_q_len == 1 ? 1 : 0;
-  // few rows (a decode step): many threads per row, so that a row's loads are in flight together
-  int threads = THREADS;
-  if (T <= 256) threads = min(1024, max(THREADS, (d / 2 + 31) / 32 * 32));
-  else if (d >= 2048) threads = 256;
-  if (out_dtype == AYK_DTYPE_F32)
-    ayk_launch(rmsnorm_conv_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)out, x, w, taps_w, state, row_req,
-               req_q_start, req_slot, d, taps, eps, inline_state);
-  else if (out_dtype == AYK_DTYPE_BF16)
-    ayk_launch(rmsnorm_conv_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
-               state, row_req, req_q_start, req_slot, d, taps, eps, inline_state);
-  else
-    return ayk_fail("ayk_rmsnorm_conv: unknown dtype %d", out_dtype);
+  const bool vec = d % 4 == 0 && d <= 4096 && (uintptr_t)taps_w % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0 && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16);
+  if (vec) {
+    // two float4 columns per thread; few rows (a decode step): one, so that a row's loads are all in flight together
+    const int nv = d / 4;
+    int threads = (((T <= 256 ? nv : (nv + 1) / 2) + 31) / 32) * 32;
+    threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+    if (out_dtype == AYK_DTYPE_F32)
+      ayk_launch(rmsnorm_conv_vec_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)out, x, w, taps_w, state, row_req,
+                 req_q_start, req_slot, d, taps, eps, inline_state);
+    else
+      ayk_launch(rmsnorm_conv_vec_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
+                 state, row_req, req_q_start, req_slot, d, taps, eps, inline_state);
+  } else {
+    // few rows (a decode step): many threads per row, so that a row's loads are in flight together
+    int threads = THREADS;
+    if (T <= 256) threads = min(1024, max(THREADS, (d / 2 + 31) / 32 * 32));
+    else if (d >= 2048) threads = 256;
+    if (out_dtype == AYK_DTYPE_F32)
+      ayk_launch(rmsnorm_conv_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)out, x, w, taps_w, state, row_req,
+                 req_q_start, req_slot, d, taps, eps, inline_state);
+    else if (out_dtype == AYK_DTYPE_BF16)
+      ayk_launch(rmsnorm_conv_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
+                 state, row_req, req_q_start, req_slot, d, taps, eps, inline_state);
+    else
+      return ayk_fail("ayk_rmsnorm_conv: unknown dtype %d", out_dtype);
+  }
   if (launched) *launched = 1;
   if (ayk_check_launch("ayk_rmsnorm_conv") != 0) return -1;
   if (!inline_state && taps > 1) {
-    ayk_launch(conv_state_kernel, dim3(R), dim3(THREADS), 0, stream, state, x, w, req_q_start, req_slot, d, taps, eps);
+    // one block per request: as many threads as channels (up to 1,024), so that its few loads are in flight together
+    const int st_threads = d >= 1024 ? 1024 : (d + 31) / 32 * 32;
+    ayk_launch(conv_state_kernel, dim3(R), dim3(st_threads), 0, stream, state, x, w, req_q_start, req_slot, d, taps, eps);
     if (launched) *launched = 2;
     return ayk_check_launch("ayk_rmsnorm_conv (state)");
   }

@@ -320,15 +320,15 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dtype:
 def rmsnorm_conv(x: torch.Tensor, weight: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, ctx, eps: float,
                  out_dtype: torch.dtype) -> torch.Tensor:
     """h + conv(h) with h = rmsnorm(x) * weight: a causal convolution over time on every channel,
-    ``taps`` [width, n] float32 (tap j multiplies the input n - 1 - j steps back).  The last n - 1
+    ``taps`` [n, width] float32, tap-major (tap j multiplies the input n - 1 - j steps back).  The last n - 1
     inputs h of every request live in ``state`` [slots, n - 1, width] float32 and are brought up to
     date.  Rows, requests and slots come from the step context."""
     lib = _ready()
     T, d = x.shape
-    n = taps.shape[1]
+    n = taps.shape[0]
     _f32(x, "x"); _f32(weight, "weight"); _f32(taps, "taps"); _f32(state, "state")
-    if taps.shape[0] != d or state.shape[1:] != (n - 1, d):
-        raise KernelError("rmsnorm_conv: taps [width, n] and state [slots, n - 1, width] must fit the rows")
+    if taps.shape[1] != d or state.shape[1:] != (n - 1, d):
+        raise KernelError("rmsnorm_conv: taps [n, width] and state [slots, n - 1, width] must fit the rows")
     out = torch.empty((T, d), dtype=out_dtype, device=x.device)
     launched = ctypes.c_int(0)
     code = lib.ayk_rmsnorm_conv(_ptr(out), _ptr(x), _ptr(weight), _ptr(taps), _ptr(state), _ptr(ctx.row_req),

@@ -27,6 +27,11 @@ class TimeConv(Part):
     def tensors(self):
         return {"weight": TensorDecl((self.width, self.taps), "vector")}
 
+    def bind(self, tensors):
+        """The kernel reads a tap of neighbouring channels at a time: the weight is kept tap-major."""
+        super().bind(tensors)
+        self.weight_taps = self.weight.t().contiguous()           # [taps, width]
+
     def cache_need(self):
         return StateNeed((max(self.taps - 1, 1), self.width), torch.float32)
 
@@ -36,7 +41,7 @@ class TimeConv(Part):
         state = ctx.cache.state_layer(cache.group, cache.layer)
         if self.taps == 1:
             state = state[:, :0]
-        return ops.rmsnorm_conv(x, norm.weight, self.weight, state, ctx, norm.eps, self.dtype)
+        return ops.rmsnorm_conv(x, norm.weight, self.weight_taps, state, ctx, norm.eps, self.dtype)
 
 
 register_part(TimeConv.KIND, TimeConv)

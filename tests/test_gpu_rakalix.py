@@ -226,14 +226,14 @@ def test_rotary_frequencies_and_turning(scaling):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps", [1, 2, 4, 7])
-def test_time_conv_whole_in_portions_and_batched(dtype, taps):
+@pytest.mark.parametrize("taps,d", [(1, 40), (2, 30), (4, 40), (4, 35), (7, 264)])
+def test_time_conv_whole_in_portions_and_batched(dtype, taps, d):
     """The convolution's state: portions shorter than the taps, single tokens, two requests in
     one step, a slot that is used again."""
     from ayaka_py_b200.cache import CacheBinding, CacheGroupSpec
     from ayaka_py_b200.parts import PartSpec, make_part
     rs = np.random.RandomState(3)
-    d, eps = 40, 1e-5
+    eps = 1e-5
     conv = make_part(PartSpec("time_conv", {"width": d, "taps": taps}), DT[dtype], "cuda")
     norm = make_part(PartSpec("rmsnorm", {"width": d, "eps": eps}), DT[dtype], "cuda")
     w, g = rs.randn(d, taps).astype(np.float32) * 0.5, (1 + 0.1 * rs.randn(d)).astype(np.float32)
@@ -381,6 +381,88 @@ def test_poly_norm_feed_forward_part(dtype):
     res = rs.randn(11, d).astype(np.float32)
     got = part.forward(dev(h, DT[dtype]), dev(res), None)
     assert np.abs(host(got) - (res + want)).max() < tol(dtype, 3 * float(np.abs(want).max()))
+
+
+# ------------------------------------------------- the faster kernels against the plain ones --
+
+def kv_context(H, rank, rot, P, plan_lengths):
+    """A cache with one latent group filled with random pages, and a runner."""
+    from ayaka_py_b200.cache import CacheGroupSpec
+    from ayaka_py_b200.parts import KVNeed
+    cache, runner = context_for([CacheGroupSpec("g", KVNeed(1, rot, None, 1, rank), 1)], "bfloat16", max_requests=4,
+                                page_size=P, pages=2048 // P, positions=1024)
+    rope, lat = cache.kv_layer(0, 0)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    lat.copy_(torch.randn(lat.shape, generator=gen, device="cuda"))
+    rope.copy_(torch.randn(rope.shape, generator=gen, device="cuda"))
+    return cache, runner, lat[:, :, 0], rope[:, :, 0]
+
+
+@pytest.mark.parametrize("H,rank,rot,P", [(4, 64, 32, 16), (16, 512, 64, 16), (6, 40, 8, 8), (40, 32, 8, 16), (1, 264, 24, 16)])
+def test_tensor_core_latent_attention_against_the_32_bit_pipes(H, rank, rot, P):
+    """Prompts, portions on top of a cached context, single rows (whose context is cut into
+    partitions and merged), all in one cache: both kernels read the same pages."""
+    from ayaka_py_b200 import ops
+    cache, runner, lat, rope = kv_context(H, rank, rot, P, None)
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    for plan in ({0: 500, 1: 33, 2: 1}, {0: 7, 2: 130}, {0: 1, 1: 1, 2: 1}, {1: 1}, {0: 64, 1: 1, 2: 1, 3: 17}):
+        ctx, res = step_of(cache, runner, plan)
+        q = torch.randn(ctx.num_rows, H, rank + rot, generator=gen, device="cuda") * 0.5
+        a = ops.latent_attention(q, lat, rope, ctx.tables[0], ctx, 0.2, tensor_cores=False)
+        b = ops.latent_attention(q, lat, rope, ctx.tables[0], ctx, 0.2, tensor_cores=True)
+        assert not torch.isnan(b).any()
+        assert float((a - b).abs().max()) < 0.01 * float(a.abs().max()) + 1e-3, plan
+        cache.commit(res)
+
+
+@pytest.mark.parametrize("H,N,K", [(3, 24, 40), (16, 512, 128), (2, 70, 264), (5, 8, 96)])
+def test_per_head_products_on_both_pipes(H, N, K):
+    from ayaka_py_b200 import ops
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    for T in (1, 17, 130):
+        wide = torch.randn(T, H * (K + 4) + 8, generator=gen, device="cuda")
+        a = wide[:, :H * (K + 4)].view(T, H, K + 4)[:, :, :K]              # strided rows and heads
+        w = (torch.randn(H, N, K, generator=gen, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        gate = torch.randn(T, H + 3, generator=gen, device="cuda")[:, :H]
+        want = torch.einsum("thk,hnk->thn", a.double(), w.double()) * torch.sigmoid(gate.double())[:, :, None]
+        for out_dtype in (torch.float32, torch.bfloat16):
+            out = torch.zeros(T, H, N + 2, dtype=out_dtype, device="cuda")[:, :, :N]
+            ops.head_matmul(a, w, out, gate=gate)
+            assert float((out.double() - want).abs().max()) < (2e-4 if out_dtype == torch.float32 else 2e-2)
+        plain_out = torch.empty(T, H, N, device="cuda")
+        ops.head_matmul(a, w.float(), plain_out)                            # 32-bit weights: the FP32 pipes
+        assert float((plain_out.double() - torch.einsum("thk,hnk->thn", a.double(), w.double())).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 10, 36), (1, 128, 128), (3, 33, 70)])
+def test_hgrn2_in_chunks_against_the_walk_with_strong_and_weak_decay(heads, dim, vdim):
+    """Both forms from the same projections: gates near zero (everything forgotten at once, logs
+    of tiny numbers) and near one (hundreds of tokens remembered)."""
+    from ayaka_py_b200 import ops
+    from ayaka_py_b200.cache import CacheGroupSpec
+    from ayaka_py_b200.parts import StateNeed
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    width = heads * (2 * dim + vdim)
+    for bias, lower in ((-30.0, 0.0), (0.0, 0.3), (8.0, 0.99)):
+        f_bias = torch.full((heads * dim,), bias, device="cuda")
+        low = torch.full((heads * dim,), lower, device="cuda")
+        outs = []
+        for chunked in (False, True):
+            cache, runner = context_for([CacheGroupSpec("g", StateNeed((heads, dim, vdim)), 1)], "float32", max_requests=3)
+            state = cache.state_layer(0, 0)
+            got = []
+            g2 = torch.Generator(device="cuda").manual_seed(5)
+            for plan in ({0: 37, 1: 3}, {0: 16, 1: 1, 2: 50}, {0: 1, 2: 15}):
+                ctx, res = step_of(cache, runner, plan)
+                proj = torch.randn(ctx.num_rows, width + 4, generator=g2, device="cuda")
+                got.append(ops.hgrn2(proj, state, f_bias, low, ctx, heads, dim, vdim, chunked=chunked))
+                cache.commit(res)
+            outs.append((torch.cat(got), state.clone()))
+        (a, sa), (b, sb) = outs
+        assert not torch.isnan(b).any() and not torch.isnan(sb).any()
+        scale = float(a.abs().max()) + 1e-6
+        assert float((a - b).abs().max()) < 2e-5 * max(1.0, scale), (bias, lower)
+        assert float((sa - sb).abs().max()) < 2e-5 * max(1.0, float(sa.abs().max()))
 
 
 # --------------------------------------------------------------- whole models --
