@@ -284,7 +284,7 @@ conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, const 
       }
     }
   }
-  block_sums_any<MAX_TAPS>(sums, red);
+  block_sums_upto<MAX_TAPS>(sums, red, back);
   float* st = state + (size_t)slot * back * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float fresh[MAX_TAPS];

@@ -9,7 +9,7 @@ regions of exactly K steps each, repeated until at least 64 steps are timed
 (``config.timed_steps``).  ``e2e`` is the same through the engine's public loop
 (scheduler, cache manager, step, sampling) by the wall clock, with the step's
 tokens copied in from pinned host memory and the sampled tokens read back every
-step.  One JSON line is printed; besides the contract's keys it carries
+step.  One JSON line is printed; besides the required keys it carries
 
 * ``prefill``: 2 prompts x 1,024 ids in one step, with the fraction of the
   measured bf16 matrix peak;
