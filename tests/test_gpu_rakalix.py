@@ -226,6 +226,42 @@ def test_rotary_frequencies_and_turning(scaling):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rotary_as_the_position_encoding_of_the_paged_attention_part(dtype):
+    """The rotation is a part of its own: the engine's multi-head attention takes it through the
+    declared hook (grouped queries, fewer rotated dimensions than the head holds), whole and continued."""
+    from ayaka_py_b200.cache import CacheBinding, CacheGroupSpec
+    from ayaka_py_b200.parts import PartSpec, make_part
+    rs = np.random.RandomState(12)
+    d, H, Hkv, Dh, dims, base, scale = 48, 4, 2, 16, 12, 3000.0, 0.25
+    part = make_part(PartSpec("attention", {"width": d, "num_heads": H, "kv_heads": Hkv, "head_dim": Dh, "scale": scale,
+                                            "window": None, "bias": False}), DT[dtype], "cuda")
+    rot = make_part(PartSpec("rotary", {"dims": dims, "base": base, "scaling": ROT_SCALED["scaling"]}), DT[dtype], "cuda")
+    part.set_position(rot)
+    wq = plain.bf16_round(rs.randn((H + 2 * Hkv) * Dh, d).astype(np.float32) / np.sqrt(d))
+    wo = plain.bf16_round(rs.randn(d, H * Dh).astype(np.float32) / np.sqrt(H * Dh))
+    part.bind({"qkv_weight": dev(wq, DT[dtype]), "out_weight": dev(wo, DT[dtype])})
+    n = 45
+    h = plain.bf16_round(rs.randn(n, d).astype(np.float32))
+    qkv = h.astype(np.float64) @ wq.astype(np.float64).T
+    pos = np.arange(n)
+    q = plain.rotate(qkv[:, :H * Dh].reshape(n, H, Dh), pos, dims, base, ROT_SCALED["scaling"])
+    k = plain.rotate(qkv[:, H * Dh:(H + Hkv) * Dh].reshape(n, Hkv, Dh), pos, dims, base, ROT_SCALED["scaling"])
+    v = qkv[:, (H + Hkv) * Dh:].reshape(n, Hkv, Dh)
+    o = np.zeros((n, H, Dh))
+    for head in range(H):
+        sc = q[:, head] @ k[:, head // (H // Hkv)].T * scale
+        sc = np.where(np.tril(np.ones((n, n), dtype=bool)), sc, -np.inf)
+        w = np.exp(sc - sc.max(axis=1, keepdims=True))
+        o[:, head] = (w / w.sum(axis=1, keepdims=True)) @ v[:, head // (H // Hkv)]
+    want = o.reshape(n, H * Dh) @ wo.astype(np.float64).T
+    cache, runner = context_for([CacheGroupSpec("g", part.cache_need(), 1)], dtype, page_size=8)
+    binding = CacheBinding(0, "g", 0, True)
+    fn = lambda ctx, x: part.forward(x.contiguous(), torch.zeros(x.shape[0], d, device="cuda"), ctx, binding)
+    got = run_cut(cache, runner, {0: dev(h, DT[dtype])}, cuts_for({0: n}, [17, 2, 1, 9, 16]), fn)[0]
+    assert np.abs(got - want).max() < tol(dtype, 3 * float(np.abs(want).max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("taps,d", [(1, 40), (2, 30), (4, 40), (4, 35), (7, 264)])
 def test_time_conv_whole_in_portions_and_batched(dtype, taps, d):
     """The convolution's state: portions shorter than the taps, single tokens, two requests in
