@@ -9,7 +9,7 @@
 //   online softmax in registers (exp2, running maximum and sum per pair)
 //   O += P C       the key tile's first rank columns are the values
 // A warp owns 16 pairs and RPW columns of O (accumulators in registers); when the latent is wider
-// than RPW, CG warps share the pairs, each computing S again for its columns.  With one row per
+// than RPW, two warps share the pairs: each computes S for half of the tile's positions and hands it to the other.  With one row per
 // request (decoding) a block has WM = 1 and the context is cut into partitions of PART positions
 // (grid.z) whose partial results (maximum, sum, unnormalised O) a second kernel merges.
 //
@@ -92,6 +92,7 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [AQ][ld]
   __nv_bfloat16* Ks = Qs + AQ * ld;                                    // two buffers of [NK][ld]
   int* there = reinterpret_cast<int*>(Ks + 2 * NK * ld);                // per buffer and position: is it cached (a page, inside the range)
+  float* shared_scores = reinterpret_cast<float*>(there + 2 * NK);      // CG = 2: per warp 2 x 4 x 32 scores for its partner
   const int* my_table = table + (size_t)req * table_stride;
 
   pdl_wait();
@@ -168,20 +169,51 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
     const __nv_bfloat16* Kt = Kbuf[it & 1];
     const int* cached = there + (it & 1) * NK;
 
-    // S = Q K^T for the warp's 16 pairs and the tile's 32 positions
+    // S = Q K^T for the warp's 16 pairs and the tile's 32 positions.  Two warps that share their pairs
+    // (CG = 2) each take 16 of the positions and hand the other its scores through shared memory.
     float s[NK / 8][4];
 #pragma unroll
     for (int j = 0; j < NK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    if (CG == 2) {
+      float own[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, other[2][4];
 #pragma unroll 4
-    for (int ks = 0; ks < Dp; ks += 16) {
-      uint32_t a[4];
-      ldmatrix_x4(a, Qs + (wm * 16 + (lane & 15)) * ld + ks + (lane >> 4) * 8);
+      for (int ks = 0; ks < Dp; ks += 16) {
+        uint32_t a[4], b[4];
+        ldmatrix_x4(a, Qs + (wm * 16 + (lane & 15)) * ld + ks + (lane >> 4) * 8);
+        ldmatrix_x4(b, Kt + (cg * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + ks + ((lane >> 3) & 1) * 8);
+        mma_bf16(own[0], a, b[0], b[1]);
+        mma_bf16(own[1], a, b[2], b[3]);
+      }
+      float* mine = shared_scores + ((wm * 2 + cg) * 2) * 128;          // [2 tiles of 8 positions][4 values][32 lanes]
+      const float* theirs = shared_scores + ((wm * 2 + (1 - cg)) * 2) * 128;
 #pragma unroll
-      for (int jp = 0; jp < NK / 16; ++jp) {
-        uint32_t b[4];
-        ldmatrix_x4(b, Kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + ks + ((lane >> 3) & 1) * 8);
-        mma_bf16(s[2 * jp], a, b[0], b[1]);
-        mma_bf16(s[2 * jp + 1], a, b[2], b[3]);
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mine[(j * 4 + e) * 32 + lane] = own[j][e];
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + wm) : "memory");      // the two warps of this group of pairs
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) other[j][e] = theirs[(j * 4 + e) * 32 + lane];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] = cg == 0 ? own[j][e] : other[j][e];
+          s[2 + j][e] = cg == 0 ? other[j][e] : own[j][e];
+        }
+    } else {
+#pragma unroll 4
+      for (int ks = 0; ks < Dp; ks += 16) {
+        uint32_t a[4];
+        ldmatrix_x4(a, Qs + (wm * 16 + (lane & 15)) * ld + ks + (lane >> 4) * 8);
+#pragma unroll
+        for (int jp = 0; jp < NK / 16; ++jp) {
+          uint32_t b[4];
+          ldmatrix_x4(b, Kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + ks + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * jp], a, b[0], b[1]);
+          mma_bf16(s[2 * jp + 1], a, b[2], b[3]);
+        }
       }
     }
     // scale, mask, running maximum
@@ -378,7 +410,7 @@ int launch(float* out, float* partial, const float* query, const void* latent_pa
   const int HG = H < AQ ? H : AQ;
   const int BR = AQ / HG;
   const int Dp = (rank + rot + 15) & ~15;
-  const size_t smem = (size_t)(AQ + 2 * NK) * (Dp + 8) * sizeof(__nv_bfloat16) + 2 * NK * sizeof(int);
+  const size_t smem = (size_t)(AQ + 2 * NK) * (Dp + 8) * sizeof(__nv_bfloat16) + 2 * NK * sizeof(int) + (CG == 2 ? (size_t)WM * 2 * 2 * 128 * sizeof(float) : 0);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
     cudaError_t err = cudaFuncSetAttribute(latent_attention_mma_kernel<RPW, CG, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
