@@ -583,6 +583,37 @@ def test_the_batch_does_not_change_a_request(models):
     assert worst < 2e-5
 
 
+@pytest.mark.parametrize("kind", ["recurrent_only", "latent_only"])
+def test_models_of_one_kind_of_layer(tmp_path, kind):
+    """Only state slots and no pages at all, or only pages: replayed mixed and generated from through the engine."""
+    from ayaka_py_b200.engine.llm import LLM
+    from ayaka_py_b200.engine.request import StopCriteria
+    from ayaka_py_b200.sampling.params import SamplingParams
+    layers = ([recurrent(2, 12, 20, 40), recurrent(1, 8, 48, None)] if kind == "recurrent_only"
+              else [latent(2, 12, 8, 20, 16, ROT_PLAIN, 0.3, None), latent(3, 8, 8, 8, 24, ROT_SCALED | {"dims": 8}, 0.35, 40)])
+    cfg = {"architecture": "Rakalix", "vocab": 90, "width": 40, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+           "embedding": {"scale": 2.0}, "residual_mult": 0.6, "layers": layers}
+    tensors = plain.random_tensors(cfg, seed=77)
+    folder = plain.write_folder(tmp_path / kind, cfg, tensors)
+    t64 = {k: v.astype(np.float64) for k, v in tensors.items()}
+    rs = np.random.RandomState(13)
+    reqs = {f"q{i}": rs.randint(0, 90, n).tolist() for i, n in enumerate([40, 9, 70, 23, 55])}
+    want = {rid: plain.forward(cfg, t64, toks) for rid, toks in reqs.items()}
+    trace = trace_tools.mixed(reqs, seed=5)
+    outputs, session = replay(folder, "float32", trace, 16)
+    assert trace_tools.first_difference(trace_tools.collect(trace, outputs), want, 1e-4) is None
+    kinds = {type(g.need).__name__ for g in session.model.groups}
+    assert kinds == ({"StateNeed"} if kind == "recurrent_only" else {"StateNeed", "KVNeed"})
+    llm = LLM(folder, dtype="float32", kv_pages=12, page_size=16, max_requests=2, max_model_len=96)
+    prompts = [reqs["q1"], reqs["q3"], reqs["q0"][:30]]
+    for prompt, result in zip(prompts, llm.generate(prompts, SamplingParams(temperature=0.0), StopCriteria(max_tokens=6, ignore_eos=True))):
+        want_tokens = plain.greedy_generate(cfg, t64, prompt, 6)
+        k = next((i for i, (a, b) in enumerate(zip(result.token_ids, want_tokens)) if a != b), None)
+        if k is not None:                     # a near tie may turn a token
+            logits = plain.forward(cfg, t64, prompt + want_tokens[:k])[-1]
+            assert abs(logits[result.token_ids[k]] - logits[want_tokens[k]]) < 1e-3
+
+
 # --------------------------------------------- the engine's own entry point --
 
 @pytest.mark.parametrize("graphs", [True, False])
