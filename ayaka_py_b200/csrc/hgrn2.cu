@@ -116,9 +116,10 @@ int launch(float* out, float* state, const float* proj, int proj_stride, const f
 // Two kernels.  hgrn2_chunk_prepare: one block per (chunk of 16 tokens, head), all chunks side by
 // side: gates, running log-decays, and per chunk the decayed queries Q' = q e^b, the write weights
 // K' = k e^(b_last - b), the chunk's decay e^(b_last) and the 16 x 16 matrix A, into scratch.
-// hgrn2_chunk_scan: one block per (request, head, 32 value columns) walks the request's chunks in
-// order, the state in registers: o = Q'^T S + A v, then S = diag(e^(b_last)) S + K' v^T.
-constexpr int CT = 16, SW = 8;      // tokens per chunk; warps of the walk over chunks (each holds an eighth of the state's rows)
+// hgrn2_chunk_scan: one block per (request, head, 16 value columns) walks the request's chunks in
+// order, the state in registers (8 warps x 2 halves hold 16 slices of its rows): o = Q'^T S + A v, then S = diag(e^(b_last)) S + K' v^T.
+constexpr int CT = 16, SW = 8, SC = 16;   // tokens per chunk; warps of the walk over chunks; value columns of one of its blocks
+static_assert(2 * SW == CT, "each half warp finishes one token of a chunk");
 
 // floats of scratch per (chunk, head): Q' and K' [dim][CT], the decay [dim rounded up to 4], A [CT][CT]; a multiple of 4
 __host__ __device__ inline size_t chunk_floats(int dim) { return (size_t)2 * CT * dim + ((dim + 3) & ~3) + CT * CT; }
@@ -218,19 +219,21 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
                         const int* __restrict__ req_slot, int H, int dim, int vdim) {
   extern __shared__ __align__(16) float smem[];
   const size_t per_chunk = chunk_floats(dim);              // a multiple of 4 floats
-  float* stage[2] = {smem, smem + per_chunk + CT * COLS};  // per buffer: the chunk's scratch, then v [CT][COLS]
-  float* red = smem + 2 * (per_chunk + CT * COLS);         // [SW][CT][COLS]
+  float* stage[2] = {smem, smem + per_chunk + CT * SC};    // per buffer: the chunk's scratch, then v [CT][SC]
+  float* red = smem + 2 * (per_chunk + CT * SC);           // [SW][CT][SC]
   pdl_trigger();
-  const int req = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
+  const int req = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * SC;
   const int first = req_q_start[req], n = req_q_start[req + 1] - first;
   const int slot = req_slot[req];
   int chunk0 = 0;                                          // global number of the request's first chunk
   for (int r = 0; r < req; ++r) chunk0 += (req_q_start[r + 1] - req_q_start[r] + CT - 1) / CT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = c0 + lane;
+  // a block has 16 value columns; a warp's two halves hold different rows of the state: 16 slices of rows
+  const int colj = lane & 15, half = lane >> 4;
+  const int col = c0 + colj;
   const bool col_ok = col < vdim;
-  const int per = (dim + SW - 1) / SW;
-  const int i0 = warp * per;
+  const int per = (dim + 2 * SW - 1) / (2 * SW);
+  const int i0 = (warp * 2 + half) * per;
   const int vcol = 2 * H * dim + h * vdim;
   pdl_wait();
   float* S = state + ((size_t)slot * H + h) * dim * vdim;
@@ -246,8 +249,8 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
     for (int i = threadIdx.x; i < (int)(per_chunk / 4); i += blockDim.x) cp_async_16(dst + 4 * i, src + 4 * i);
     float* v = dst + per_chunk;
     const int steps = min(CT, n - c * CT);
-    for (int i = threadIdx.x; i < CT * COLS; i += blockDim.x) {
-      const int tt = i / COLS, cc = i - tt * COLS;
+    for (int i = threadIdx.x; i < CT * SC; i += blockDim.x) {
+      const int tt = i / SC, cc = i - tt * SC;
       if (tt < steps && c0 + cc < vdim) cp_async_4(v + i, proj + (size_t)(first + c * CT + tt) * proj_stride + vcol + c0 + cc);
       else v[i] = 0.f;
     }
@@ -265,7 +268,7 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
     const int steps = min(CT, n - c * CT);
     float acc[CT], v[CT];
 #pragma unroll
-    for (int tt = 0; tt < CT; ++tt) { acc[tt] = 0.f; v[tt] = vs[tt * COLS + lane]; }
+    for (int tt = 0; tt < CT; ++tt) { acc[tt] = 0.f; v[tt] = vs[tt * SC + colj]; }
 #pragma unroll
     for (int i = 0; i < DP; ++i) {
       if (i < per && i0 + i < dim) {
@@ -289,15 +292,21 @@ hgrn2_chunk_scan_kernel(float* __restrict__ out, float* __restrict__ state, cons
       }
     }
 #pragma unroll
-    for (int tt = 0; tt < CT; ++tt) red[(warp * CT + tt) * COLS + lane] = acc[tt];
+    for (int tt = 0; tt < CT; ++tt) {
+      acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], 16);       // the warp's two halves
+      if (half == 0) red[(warp * CT + tt) * SC + colj] = acc[tt];
+    }
     __syncthreads();
-    // warp w finishes tokens w and w + 8: the warps' partial sums (in order) plus what the chunk itself wrote
-    for (int tt = warp; tt < steps; tt += SW) {
-      float o = 0.f;
+    // each half warp finishes one token: the warps' partial sums (in order) plus what the chunk itself wrote
+    {
+      const int tt = warp * 2 + half;
+      if (tt < steps) {
+        float o = 0.f;
 #pragma unroll
-      for (int w8 = 0; w8 < SW; ++w8) o += red[(w8 * CT + tt) * COLS + lane];
-      for (int sidx = 0; sidx <= tt; ++sidx) o = fmaf(As[tt * CT + sidx], vs[sidx * COLS + lane], o);
-      if (col_ok) out[(size_t)(first + c * CT + tt) * ((size_t)H * vdim) + h * vdim + col] = o;
+        for (int w8 = 0; w8 < SW; ++w8) o += red[(w8 * CT + tt) * SC + colj];
+        for (int sidx = 0; sidx <= tt; ++sidx) o = fmaf(As[tt * CT + sidx], vs[sidx * SC + colj], o);
+        if (col_ok) out[(size_t)(first + c * CT + tt) * ((size_t)H * vdim) + h * vdim + col] = o;
+      }
     }
     __syncthreads();        // the buffer and red are free for the chunk after the next
   }
@@ -313,7 +322,7 @@ int launch_chunk(float* out, float* state, float* scratch, const float* proj, in
                  const float* lower, const int* req_q_start, const int* req_slot, int R, int T, int H, int dim, int vdim,
                  cudaStream_t stream) {
   const size_t smem_p = (size_t)3 * CT * (dim + 1) * sizeof(float);
-  const size_t smem_s = (2 * (chunk_floats(dim) + CT * COLS) + (size_t)SW * CT * COLS) * sizeof(float);
+  const size_t smem_s = (2 * (chunk_floats(dim) + CT * SC) + (size_t)SW * CT * SC) * sizeof(float);
   static size_t configured_p = 48 * 1024, configured_s = 48 * 1024;
   if (smem_p > configured_p) {
     cudaError_t err = cudaFuncSetAttribute(hgrn2_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
@@ -328,7 +337,7 @@ int launch_chunk(float* out, float* state, float* scratch, const float* proj, in
   ayk_launch(hgrn2_chunk_prepare_kernel, dim3(T / CT + R, H), dim3(128), smem_p, stream, scratch, proj, proj_stride, f_bias,
              lower, req_q_start, R, H, dim);
   if (ayk_check_launch("ayk_hgrn2 (chunk prepare)") != 0) return -1;
-  ayk_launch(hgrn2_chunk_scan_kernel<DP>, dim3((vdim + COLS - 1) / COLS, H, R), dim3(SW * 32), smem_s, stream, out, state,
+  ayk_launch(hgrn2_chunk_scan_kernel<DP>, dim3((vdim + SC - 1) / SC, H, R), dim3(SW * 32), smem_s, stream, out, state,
              (const float*)scratch, proj, proj_stride, req_q_start, req_slot, H, dim, vdim);
   return ayk_check_launch("ayk_hgrn2 (chunk scan)");
 }
@@ -348,13 +357,13 @@ AYK_EXPORT int ayk_hgrn2(float* out, float* state, const float* proj, int proj_s
   AYK_REQUIRE(H <= 65535 && R <= 65535, "ayk_hgrn2: too many heads or requests");
   const int per = (dim + WARPS - 1) / WARPS;
   if (scratch) {
-    const int per8 = (dim + SW - 1) / SW;
+    const int per8 = (dim + 2 * SW - 1) / (2 * SW);      // rows of the state per thread: 16 slices
 #define AYK_HC(DP) return launch_chunk<DP>(out, state, scratch, proj, proj_stride, f_bias, lower, req_q_start, req_slot, R, T, H, dim, vdim, stream)
+    if (per8 <= 2) AYK_HC(2);
     if (per8 <= 4) AYK_HC(4);
     if (per8 <= 8) AYK_HC(8);
     if (per8 <= 16) AYK_HC(16);
-    if (per8 <= 32) AYK_HC(32);
-    AYK_HC(64);
+    AYK_HC(32);
 #undef AYK_HC
   }
 #define AYK_HG(DP) return launch<DP>(out, state, proj, proj_stride, f_bias, lower, req_q_start, req_slot, R, H, dim, vdim, stream)
