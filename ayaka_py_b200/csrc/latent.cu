@@ -157,6 +157,70 @@ head_matmul_kernel(O* __restrict__ out, long long out_row, int out_head, const f
   }
 }
 
+
+// The same product for a handful of rows (a decode step): a block takes one head and eight output
+// columns, one per warp; the rows' operand of that head sits in shared memory, a warp streams its
+// weight row once (eight elements per lane and step) and keeps one sum per row.
+constexpr int MV_ROWS = 16, MV_WARPS = 8;
+
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __bfloat162float(h[i].x); v[2 * i + 1] = __bfloat162float(h[i].y); }
+}
+
+template <typename W, typename O>
+__global__ void __launch_bounds__(MV_WARPS * 32)
+head_matvec_kernel(O* __restrict__ out, long long out_row, int out_head, const float* __restrict__ a, long long a_row,
+                   int a_head, const W* __restrict__ w, const float* __restrict__ gate, long long gate_row, int T, int N,
+                   int K) {
+  extern __shared__ __align__(16) float rows[];          // [T][K]
+  pdl_trigger();
+  const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y * MV_WARPS + warp;
+  // the weight row does not depend on the kernel before: its first piece is asked for ahead of the wait
+  const W* wr = w + ((size_t)h * N + (n < N ? n : 0)) * K;
+  float w8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (lane * 8 < K) load8(wr + lane * 8, w8);
+  pdl_wait();
+  for (int i = threadIdx.x; i < T * (K / 4); i += blockDim.x) {
+    const int t = i / (K / 4), c = (i - t * (K / 4)) * 4;
+    *reinterpret_cast<float4*>(rows + t * K + c) = *reinterpret_cast<const float4*>(a + (size_t)t * a_row + (size_t)h * a_head + c);
+  }
+  __syncthreads();
+  if (n >= N) return;
+  float acc[MV_ROWS];
+#pragma unroll
+  for (int t = 0; t < MV_ROWS; ++t) acc[t] = 0.f;
+  for (int k0 = lane * 8; k0 < K; k0 += 256) {
+    if (k0 != lane * 8) load8(wr + k0, w8);
+#pragma unroll
+    for (int t = 0; t < MV_ROWS; ++t) {
+      if (t < T) {
+        float a8[8];
+        load8(rows + t * K + k0, a8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[t] = fmaf(a8[e], w8[e], acc[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < MV_ROWS; ++t) {
+    if (t < T) {
+      float v = warp_sum(acc[t]);
+      if (lane == 0) {
+        if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + h]));
+        out[(size_t)t * out_row + (size_t)h * out_head + n] = from_float<O>(v);
+      }
+    }
+  }
+}
+
 // --------------------------------------------------------------- attention --
 // One block: up to 32 (row, head) pairs of one request: BR consecutive rows x HG heads.  Keys are
 // taken 32 at a time; lane j scores key j; for the weighted sum lane l owns latent columns l, l+32...
@@ -405,4 +469,37 @@ AYK_EXPORT int ayk_latent_attention(float* out, const float* query, const void* 
     return pick_latent_attention<__nv_bfloat16>(out, query, latent_pages, rope_pages, table, table_stride, req_q_start,
                                                 req_pos0, num_req, total_rows, H, rank, rot, page_size, scale, stream);
   return ayk_fail("ayk_latent_attention: unknown dtype %d", cache_dtype);
+}
+
+// The per-head product for up to 16 rows (ayk_head_matvec_takes): K a multiple of 8, 16-byte aligned operands.
+AYK_EXPORT int ayk_head_matvec_takes(const void* a, long long a_row, int a_head, const void* w, int T, int K) {
+  return T >= 1 && T <= MV_ROWS && K % 8 == 0 && (size_t)T * K * 4 <= 96 * 1024 && a_row % 4 == 0 && a_head % 4 == 0 &&
+         (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0;
+}
+
+AYK_EXPORT int ayk_head_matvec(void* out, long long out_row, int out_head, const float* a, long long a_row, int a_head,
+                               const void* w, const float* gate, long long gate_row, int T, int H, int N, int K, int w_dtype,
+                               int out_dtype, cudaStream_t stream) {
+  if (T == 0 || H == 0 || N == 0) return 0;
+  AYK_REQUIRE(ayk_head_matvec_takes(a, a_row, a_head, w, T, K), "ayk_head_matvec: %d rows of %d are not taken", T, K);
+  dim3 grid(H, (N + MV_WARPS - 1) / MV_WARPS);
+  AYK_REQUIRE(grid.y <= 65535, "ayk_head_matvec: too many columns");
+  const size_t smem = (size_t)T * K * sizeof(float);
+#define AYK_MV(WT, OT)                                                                                                         \
+  do {                                                                                                                         \
+    static size_t configured = 48 * 1024;                                                                                      \
+    if (smem > configured) {                                                                                                   \
+      cudaError_t err = cudaFuncSetAttribute(head_matvec_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (err != cudaSuccess) return ayk_fail("ayk_head_matvec: shared memory %zu: %s", smem, cudaGetErrorString(err));        \
+      configured = smem;                                                                                                       \
+    }                                                                                                                          \
+    ayk_launch(head_matvec_kernel<WT, OT>, grid, dim3(MV_WARPS * 32), smem, stream, (OT*)out, out_row, out_head, a, a_row,     \
+               a_head, (const WT*)w, gate, gate_row, T, N, K);                                                                 \
+  } while (0)
+  if (w_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32) AYK_MV(float, float);
+  else if (w_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_F32) AYK_MV(__nv_bfloat16, float);
+  else if (w_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_BF16) AYK_MV(__nv_bfloat16, __nv_bfloat16);
+  else return ayk_fail("ayk_head_matvec: unsupported dtypes w=%d out=%d", w_dtype, out_dtype);
+#undef AYK_MV
+  return ayk_check_launch("ayk_head_matvec");
 }

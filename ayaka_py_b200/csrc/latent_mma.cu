@@ -303,24 +303,42 @@ latent_attention_mma_kernel(float* __restrict__ out, float* __restrict__ partial
   }
 }
 
-// out[pair, :] = sum_p exp2(m_p - m) O_p / sum_p exp2(m_p - m) l_p, partitions in order.
+// out[pair, :] = sum_p exp2(m_p - m) O_p / sum_p exp2(m_p - m) l_p, partitions in order.  The
+// partitions' maxima and sums are fetched side by side first; a partition that saw nothing is skipped.
+constexpr int MERGE_PARTS = 1024;
 __global__ void latent_merge_kernel(float* __restrict__ out, const float* __restrict__ partial, int rank, int parts) {
+  __shared__ float weight[MERGE_PARTS];
+  __shared__ float total[2];
   pdl_trigger();
   pdl_wait();
   const float* src = partial + (size_t)blockIdx.x * parts * (rank + 2);
-  float m = -INFINITY;
-  for (int p = 0; p < parts; ++p) m = fmaxf(m, src[(size_t)p * (rank + 2)]);
-  float l = 0.f;
-  for (int p = 0; p < parts; ++p) {
-    const float mp = src[(size_t)p * (rank + 2)];
-    if (mp > -INFINITY) l += exp2f(mp - m) * src[(size_t)p * (rank + 2) + 1];
+  for (int p = threadIdx.x; p < parts; p += blockDim.x) weight[p] = src[(size_t)p * (rank + 2)];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = -INFINITY;
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, weight[p]);
+    total[0] = m;
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __syncthreads();
+  const float m = total[0];
+  for (int p = threadIdx.x; p < parts; p += blockDim.x) {
+    const float mp = weight[p];
+    weight[p] = mp > -INFINITY ? exp2f(mp - m) : 0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float l = 0.f;
+    for (int p = 0; p < parts; ++p)
+      if (weight[p] > 0.f) l = fmaf(weight[p], src[(size_t)p * (rank + 2) + 1], l);
+    total[1] = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
+  const float inv = total[1];
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float acc = 0.f;
     for (int p = 0; p < parts; ++p) {
-      const float mp = src[(size_t)p * (rank + 2)];
-      if (mp > -INFINITY) acc = fmaf(exp2f(mp - m), src[(size_t)p * (rank + 2) + 2 + d], acc);
+      const float wp = weight[p];
+      if (wp > 0.f) acc = fmaf(wp, src[(size_t)p * (rank + 2) + 2 + d], acc);
     }
     out[(size_t)blockIdx.x * rank + d] = acc * inv;
   }
@@ -442,7 +460,7 @@ AYK_EXPORT int ayk_latent_attention_mma(float* out, float* partial, const float*
   if (num_req == 0 || total_rows == 0) return 0;
   AYK_REQUIRE(ayk_latent_attention_mma_takes(rank, rot), "ayk_latent_attention_mma: latent %d + %d is not taken", rank, rot);
   AYK_REQUIRE(parts == 1 || max_q_len == 1, "ayk_latent_attention_mma: the context is cut only for single rows");
-  AYK_REQUIRE(parts >= 1 && parts <= 65535 && (parts == 1 || part_keys % NK == 0), "ayk_latent_attention_mma: %d partitions of %d", parts, part_keys);
+  AYK_REQUIRE(parts >= 1 && parts <= MERGE_PARTS && (parts == 1 || part_keys % NK == 0), "ayk_latent_attention_mma: %d partitions of %d", parts, part_keys);
   const bool single = max_q_len == 1 && H <= 16;
   int rc;
 #define AYK_LM(RPW, CG)                                                                                                     \

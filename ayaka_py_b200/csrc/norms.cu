@@ -201,6 +201,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
   const int nv = d >> 2, back = taps - 1;
   pdl_wait();
   const float4* x4 = reinterpret_cast<const float4*>(x);
+  float4* st4 = reinterpret_cast<float4*>(state + (size_t)slot * back * d);
   float4 xv[MAX_TAPS][V];
   float sums[MAX_TAPS];
 #pragma unroll
@@ -210,9 +211,13 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
     for (int v = 0; v < V; ++v) {
       const int idx = threadIdx.x + v * blockDim.x;
       xv[j][v] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (j <= back && t - j >= first && idx < nv) {
-        xv[j][v] = x4[(size_t)(t - j) * nv + idx];
-        sums[j] += (xv[j][v].x * xv[j][v].x + xv[j][v].y * xv[j][v].y) + (xv[j][v].z * xv[j][v].z + xv[j][v].w * xv[j][v].w);
+      if (j <= back && idx < nv) {
+        if (t - j >= first) {
+          xv[j][v] = x4[(size_t)(t - j) * nv + idx];
+          sums[j] += (xv[j][v].x * xv[j][v].x + xv[j][v].y * xv[j][v].y) + (xv[j][v].z * xv[j][v].z + xv[j][v].w * xv[j][v].w);
+        } else {
+          xv[j][v] = st4[(size_t)(back + (t - j - first)) * nv + idx];     // an input of an earlier step: normed already
+        }
       }
     }
   }
@@ -220,7 +225,6 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
   float inv[MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < MAX_TAPS; ++j) inv[j] = j <= back ? 1.0f / sqrtf(sums[j] / (float)d + eps) : 0.f;
-  float4* st4 = reinterpret_cast<float4*>(state + (size_t)slot * back * d);
 #pragma unroll
   for (int v = 0; v < V; ++v) {
     const int idx = threadIdx.x + v * blockDim.x;
@@ -233,7 +237,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
       if (j <= back) {
         const int s = t - j;
         if (s >= first) h[j] = make_float4(xv[j][v].x * inv[j] * wi.x, xv[j][v].y * inv[j] * wi.y, xv[j][v].z * inv[j] * wi.z, xv[j][v].w * inv[j] * wi.w);
-        else h[j] = st4[(size_t)(back + (s - first)) * nv + idx];
+        else h[j] = xv[j][v];
       }
     }
     float acc[4];

@@ -419,8 +419,12 @@ def head_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch
               ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), _ptr(gate),
               ctypes.c_longlong(gate.stride(0) if gate is not None else 0), ctypes.c_int(T), ctypes.c_int(H),
               ctypes.c_int(N), ctypes.c_int(K))
-    # bfloat16 weights: the tensor cores, the float32 operand rounded on its way in; else the FP32 pipes
-    if w.dtype == torch.bfloat16 and lib.ayk_head_matmul_mma_takes(_ptr(a), ctypes.c_longlong(a.stride(0)),
+    # a handful of rows (a decode step): a warp per output column streams its weight row once
+    if lib.ayk_head_matvec_takes(_ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), ctypes.c_int(T),
+                                 ctypes.c_int(K)):
+        _launch(lib.ayk_head_matvec(*common, ctypes.c_int(_tag(w.dtype)), ctypes.c_int(_tag(out.dtype)), _stream()))
+    # bfloat16 weights: the tensor cores, the float32 operand in two bfloat16 parts; else the FP32 pipes
+    elif w.dtype == torch.bfloat16 and lib.ayk_head_matmul_mma_takes(_ptr(a), ctypes.c_longlong(a.stride(0)),
                                                                    ctypes.c_int(a.stride(1)), ctypes.c_int(K)):
         _launch(lib.ayk_head_matmul_mma(*common, ctypes.c_int(_tag(out.dtype)), _stream()))
     else:
