@@ -109,7 +109,8 @@ rmsnorm_kernel(O* __restrict__ out, long long out_stride, const float* __restric
 // from x.  One block per row.  ``inline_state``: every request of the step brings one row, and the
 // block shifts the request's state itself (each thread owns its channels, so nothing races);
 // otherwise conv_state_kernel runs afterwards.
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 16;     // the general kernels; the float4 kernel keeps rows in registers and takes up to VEC_TAPS
+constexpr int VEC_TAPS = 8;
 
 template <typename O>
 __global__ void __launch_bounds__(1024)
@@ -191,7 +192,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
                         const float* __restrict__ taps_w, float* __restrict__ state, const int* __restrict__ row_req,
                         const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps,
                         int inline_state) {
-  __shared__ float red[32 * MAX_TAPS];
+  __shared__ float red[32 * VEC_TAPS];
   constexpr int V = 2;
   pdl_trigger();
   const int t = blockIdx.x;
@@ -202,10 +203,10 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
   pdl_wait();
   const float4* x4 = reinterpret_cast<const float4*>(x);
   float4* st4 = reinterpret_cast<float4*>(state + (size_t)slot * back * d);
-  float4 xv[MAX_TAPS][V];
-  float sums[MAX_TAPS];
+  float4 xv[VEC_TAPS][V];
+  float sums[VEC_TAPS];
 #pragma unroll
-  for (int j = 0; j < MAX_TAPS; ++j) {
+  for (int j = 0; j < VEC_TAPS; ++j) {
     sums[j] = 0.f;
 #pragma unroll
     for (int v = 0; v < V; ++v) {
@@ -221,19 +222,19 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
       }
     }
   }
-  block_sums_upto<MAX_TAPS>(sums, red, taps);
-  float inv[MAX_TAPS];
+  block_sums_upto<VEC_TAPS>(sums, red, taps);
+  float inv[VEC_TAPS];
 #pragma unroll
-  for (int j = 0; j < MAX_TAPS; ++j) inv[j] = j <= back ? 1.0f / sqrtf(sums[j] / (float)d + eps) : 0.f;
+  for (int j = 0; j < VEC_TAPS; ++j) inv[j] = j <= back ? 1.0f / sqrtf(sums[j] / (float)d + eps) : 0.f;
 #pragma unroll
   for (int v = 0; v < V; ++v) {
     const int idx = threadIdx.x + v * blockDim.x;
     if (idx >= nv) continue;
     const float4 wi = reinterpret_cast<const float4*>(w)[idx];
-    float4 h[MAX_TAPS];
+    float4 h[VEC_TAPS];
     h[0] = make_float4(xv[0][v].x * inv[0] * wi.x, xv[0][v].y * inv[0] * wi.y, xv[0][v].z * inv[0] * wi.z, xv[0][v].w * inv[0] * wi.w);
 #pragma unroll
-    for (int j = 1; j < MAX_TAPS; ++j) {
+    for (int j = 1; j < VEC_TAPS; ++j) {
       if (j <= back) {
         const int s = t - j;
         if (s >= first) h[j] = make_float4(xv[j][v].x * inv[j] * wi.x, xv[j][v].y * inv[j] * wi.y, xv[j][v].z * inv[j] * wi.z, xv[j][v].w * inv[j] * wi.w);
@@ -246,7 +247,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
     acc[0] = h[0].x * (1.0f + t0.x); acc[1] = h[0].y * (1.0f + t0.y);
     acc[2] = h[0].z * (1.0f + t0.z); acc[3] = h[0].w * (1.0f + t0.w);
 #pragma unroll
-    for (int j = 1; j < MAX_TAPS; ++j) {
+    for (int j = 1; j < VEC_TAPS; ++j) {
       if (j <= back) {
         const float4 tj = tw4[(size_t)(back - j) * nv + idx];
         acc[0] = fmaf(tj.x, h[j].x, acc[0]); acc[1] = fmaf(tj.y, h[j].y, acc[1]);
@@ -256,7 +257,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
     store4(out + (size_t)t * d + 4 * idx, acc[0], acc[1], acc[2], acc[3]);
     if (inline_state) {
 #pragma unroll
-      for (int j = MAX_TAPS - 1; j >= 2; --j)
+      for (int j = VEC_TAPS - 1; j >= 2; --j)
         if (j <= back) st4[(size_t)(back - j) * nv + idx] = h[j - 1];
       if (back >= 1) st4[(size_t)(back - 1) * nv + idx] = h[0];
     }
@@ -393,7 +394,7 @@ AYK_EXPORT int ayk_rmsnorm_conv(void* out, const float* x, const float* w, const
   if (T == 0) return 0;
   AYK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "ayk_rmsnorm_conv: %d taps, the kernel holds up to %d", taps, MAX_TAPS);
   const int inline_state = max_q_len == 1 ? 1 : 0;
-  const bool vec = d % 4 == 0 && d <= 4096 && (uintptr_t)taps_w % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+  const bool vec = taps <= VEC_TAPS && d % 4 == 0 && d <= 4096 && (uintptr_t)taps_w % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0 &&
                    (uintptr_t)out % 16 == 0 && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16);
   if (vec) {
     // two float4 columns per thread; few rows (a decode step): one, so that a row's loads are all in flight together

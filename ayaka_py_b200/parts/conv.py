@@ -19,8 +19,8 @@ class TimeConv(Part):
     KIND = "time_conv"
 
     def __init__(self, width: int, taps: int, dtype=torch.float32, device="cuda"):
-        if not 1 <= taps <= 8:
-            raise ValueError(f"a time convolution of {taps} taps: the kernel holds 1 to 8")
+        if not 1 <= taps <= 16:
+            raise ValueError(f"a time convolution of {taps} taps: the kernels hold 1 to 16")
         self.width, self.taps, self.dtype = width, taps, dtype
         self.weight = None
 

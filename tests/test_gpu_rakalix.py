@@ -262,7 +262,7 @@ def test_rotary_as_the_position_encoding_of_the_paged_attention_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps,d", [(1, 40), (2, 30), (4, 40), (4, 35), (7, 264)])
+@pytest.mark.parametrize("taps,d", [(1, 40), (2, 30), (4, 40), (4, 35), (7, 264), (11, 48)])
 def test_time_conv_whole_in_portions_and_batched(dtype, taps, d):
     """The convolution's state: portions shorter than the taps, single tokens, two requests in
     one step, a slot that is used again."""
