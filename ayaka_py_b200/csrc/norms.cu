@@ -186,13 +186,13 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float
   *reinterpret_cast<uint2*>(p) = w;
 }
 
-template <typename O>
+template <typename O, int VT>      // VT: the most taps this instance holds rows for
 __global__ void __launch_bounds__(512, 2)
 rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                         const float* __restrict__ taps_w, float* __restrict__ state, const int* __restrict__ row_req,
                         const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int d, int taps, float eps,
                         int inline_state) {
-  __shared__ float red[32 * VEC_TAPS];
+  __shared__ float red[32 * VT];
   constexpr int V = 2;
   pdl_trigger();
   const int t = blockIdx.x;
@@ -203,10 +203,10 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
   pdl_wait();
   const float4* x4 = reinterpret_cast<const float4*>(x);
   float4* st4 = reinterpret_cast<float4*>(state + (size_t)slot * back * d);
-  float4 xv[VEC_TAPS][V];
-  float sums[VEC_TAPS];
+  float4 xv[VT][V];
+  float sums[VT];
 #pragma unroll
-  for (int j = 0; j < VEC_TAPS; ++j) {
+  for (int j = 0; j < VT; ++j) {
     sums[j] = 0.f;
 #pragma unroll
     for (int v = 0; v < V; ++v) {
@@ -222,19 +222,19 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
       }
     }
   }
-  block_sums_upto<VEC_TAPS>(sums, red, taps);
-  float inv[VEC_TAPS];
+  block_sums_upto<VT>(sums, red, taps);
+  float inv[VT];
 #pragma unroll
-  for (int j = 0; j < VEC_TAPS; ++j) inv[j] = j <= back ? 1.0f / sqrtf(sums[j] / (float)d + eps) : 0.f;
+  for (int j = 0; j < VT; ++j) inv[j] = j <= back ? 1.0f / sqrtf(sums[j] / (float)d + eps) : 0.f;
 #pragma unroll
   for (int v = 0; v < V; ++v) {
     const int idx = threadIdx.x + v * blockDim.x;
     if (idx >= nv) continue;
     const float4 wi = reinterpret_cast<const float4*>(w)[idx];
-    float4 h[VEC_TAPS];
+    float4 h[VT];
     h[0] = make_float4(xv[0][v].x * inv[0] * wi.x, xv[0][v].y * inv[0] * wi.y, xv[0][v].z * inv[0] * wi.z, xv[0][v].w * inv[0] * wi.w);
 #pragma unroll
-    for (int j = 1; j < VEC_TAPS; ++j) {
+    for (int j = 1; j < VT; ++j) {
       if (j <= back) {
         const int s = t - j;
         if (s >= first) h[j] = make_float4(xv[j][v].x * inv[j] * wi.x, xv[j][v].y * inv[j] * wi.y, xv[j][v].z * inv[j] * wi.z, xv[j][v].w * inv[j] * wi.w);
@@ -247,7 +247,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
     acc[0] = h[0].x * (1.0f + t0.x); acc[1] = h[0].y * (1.0f + t0.y);
     acc[2] = h[0].z * (1.0f + t0.z); acc[3] = h[0].w * (1.0f + t0.w);
 #pragma unroll
-    for (int j = 1; j < VEC_TAPS; ++j) {
+    for (int j = 1; j < VT; ++j) {
       if (j <= back) {
         const float4 tj = tw4[(size_t)(back - j) * nv + idx];
         acc[0] = fmaf(tj.x, h[j].x, acc[0]); acc[1] = fmaf(tj.y, h[j].y, acc[1]);
@@ -257,7 +257,7 @@ rmsnorm_conv_vec_kernel(O* __restrict__ out, const float* __restrict__ x, const 
     store4(out + (size_t)t * d + 4 * idx, acc[0], acc[1], acc[2], acc[3]);
     if (inline_state) {
 #pragma unroll
-      for (int j = VEC_TAPS - 1; j >= 2; --j)
+      for (int j = VT - 1; j >= 2; --j)
         if (j <= back) st4[(size_t)(back - j) * nv + idx] = h[j - 1];
       if (back >= 1) st4[(size_t)(back - 1) * nv + idx] = h[0];
     }
@@ -401,12 +401,15 @@ AYK_EXPORT int ayk_rmsnorm_conv(void* out, const float* x, const float* w, const
     const int nv = d / 4;
     int threads = (((T <= 256 ? nv : (nv + 1) / 2) + 31) / 32) * 32;
     threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
-    if (out_dtype == AYK_DTYPE_F32)
-      ayk_launch(rmsnorm_conv_vec_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)out, x, w, taps_w, state, row_req,
-                 req_q_start, req_slot, d, taps, eps, inline_state);
-    else
-      ayk_launch(rmsnorm_conv_vec_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)out, x, w, taps_w,
-                 state, row_req, req_q_start, req_slot, d, taps, eps, inline_state);
+#define AYK_CONV(OT, VT)                                                                                                  \
+  ayk_launch(rmsnorm_conv_vec_kernel<OT, VT>, dim3(T), dim3(threads), 0, stream, (OT*)out, x, w, taps_w, state, row_req, \
+             req_q_start, req_slot, d, taps, eps, inline_state)
+    if (out_dtype == AYK_DTYPE_F32) {
+      if (taps <= 4) AYK_CONV(float, 4); else AYK_CONV(float, VEC_TAPS);
+    } else {
+      if (taps <= 4) AYK_CONV(__nv_bfloat16, 4); else AYK_CONV(__nv_bfloat16, VEC_TAPS);
+    }
+#undef AYK_CONV
   } else {
     // few rows (a decode step): many threads per row, so that a row's loads are in flight together
     int threads = THREADS;
