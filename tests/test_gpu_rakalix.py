@@ -313,7 +313,7 @@ def bind(part, tensors, names, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("spec", [latent(3, 20, 12, 24, 40, ROT_PLAIN, 0.2, None), latent(1, 64, 32, 64, 64, ROT_SCALED, 0.1, None),
+@pytest.mark.parametrize("spec", [latent(3, 20, 12, 24, 40, ROT_PLAIN, 0.2, None), latent(1, 56, 24, 48, 72, ROT_SCALED, 0.1, None),
                                   latent(6, 8, 16, 4, 130, ROT_SCALED, 0.3, None)])
 def test_latent_attention_alone_with_keys_that_stand_out(dtype, spec):
     """Rows of the input at chosen places are made large, so that their rotated key part
@@ -434,7 +434,7 @@ def kv_context(H, rank, rot, P, plan_lengths):
     return cache, runner, lat[:, :, 0], rope[:, :, 0]
 
 
-@pytest.mark.parametrize("H,rank,rot,P", [(4, 64, 32, 16), (16, 512, 64, 16), (6, 40, 8, 8), (40, 32, 8, 16), (1, 264, 24, 16)])
+@pytest.mark.parametrize("H,rank,rot,P", [(4, 72, 24, 16), (16, 512, 64, 16), (6, 40, 8, 8), (40, 32, 8, 16), (1, 264, 24, 16)])
 def test_tensor_core_latent_attention_against_the_32_bit_pipes(H, rank, rot, P):
     """Prompts, portions on top of a cached context, single rows (whose context is cut into
     partitions and merged), all in one cache: both kernels read the same pages."""
