@@ -207,3 +207,86 @@ class RakalixConfig(ModelConfig):
         return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
                 "layers": [json.loads(json.dumps(layer)) for layer in self.layers], "norm": dict(self.norm),
                 "canon": dict(self.canon), "embedding": dict(self.embedding), "residual_mult": self.residual_mult}
+
+
+_LUPORAX_MIXERS = {"attention": ("heads", "kv_heads", "dim", "vdim"),
+                   "rglru": ("width", "blocks", "conv"),
+                   "mingru": ("width",)}
+
+
+@dataclass(frozen=True)
+class LuporaxConfig(ModelConfig):
+    """Luporax: ``layers`` lists the layer runs in order, each {"type": "attention" | "rglru" |
+    "mingru", "mixer": its sizes and constants, "mlp": {"kind": "moe", "router": {experts, top},
+    "expert": {ff, limit}, "shared": {ff, limit}} or null}; an entry with ``weights_of``: j runs
+    layer j's tensors once more, with a cache and state of its own.  ``norm.eps``,
+    ``residual_mult`` and ``logit_scale`` are the model-wide constants.  The document names the
+    design under ``architecture``.  The model has no position limit of its own."""
+
+    ARCHITECTURE: ClassVar[str] = "Luporax"
+
+    vocab: int = 0
+    width: int = 0
+    layers: tuple = ()
+    norm: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"eps": 1e-6})
+    residual_mult: float = 1.0
+    logit_scale: float = 1.0
+
+    def __post_init__(self) -> None:
+        _require_int(self.vocab, "vocab")
+        _require_int(self.width, "width")
+        if not isinstance(self.layers, (list, tuple)) or not self.layers:
+            raise ConfigError("layers must be a non-empty list")
+        object.__setattr__(self, "layers", tuple(self.layers))
+        _require_number(self.norm.get("eps") if isinstance(self.norm, Mapping) else None, "norm.eps", positive=True)
+        _require_number(self.residual_mult, "residual_mult")
+        _require_number(self.logit_scale, "logit_scale")
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, Mapping) else None
+            if kind not in _LUPORAX_MIXERS:
+                raise ConfigError(f"layers[{i}].type must be one of {sorted(_LUPORAX_MIXERS)}, got {kind!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, Mapping):
+                raise ConfigError(f"layers[{i}].mixer must give the mixer's sizes")
+            for key in _LUPORAX_MIXERS[kind]:
+                _require_int(mixer.get(key), f"layers[{i}].mixer.{key}")
+            if kind == "attention":
+                if mixer["heads"] % mixer["kv_heads"]:
+                    raise ConfigError(f"layers[{i}].mixer: {mixer['heads']} heads cannot share {mixer['kv_heads']} key/value heads")
+                _require_number(mixer.get("scale"), f"layers[{i}].mixer.scale")
+                _require_number(mixer.get("softcap"), f"layers[{i}].mixer.softcap", positive=True)
+                rot = mixer.get("rot")
+                if not isinstance(rot, Mapping):
+                    raise ConfigError(f"layers[{i}].mixer.rot must give the rotation's constants")
+                dims = _require_int(rot.get("dims"), f"layers[{i}].mixer.rot.dims")
+                _require_number(rot.get("base"), f"layers[{i}].mixer.rot.base", positive=True)
+                if dims % 2 or dims > mixer["dim"]:
+                    raise ConfigError(f"layers[{i}].mixer.rot.dims must be even and at most dim")
+            elif kind == "rglru" and mixer["width"] % mixer["blocks"]:
+                raise ConfigError(f"layers[{i}].mixer: width {mixer['width']} is not {mixer['blocks']} equal blocks")
+            source = layer.get("weights_of")
+            if source is not None:
+                _require_int(source, f"layers[{i}].weights_of", minimum=0)
+                if source >= i or "weights_of" in self.layers[source]:
+                    raise ConfigError(f"layers[{i}].weights_of must name an earlier layer that has tensors of its own")
+                mine = {k: v for k, v in layer.items() if k != "weights_of"}
+                if json.dumps(mine, sort_keys=True) != json.dumps(dict(self.layers[source]), sort_keys=True):
+                    raise ConfigError(f"layers[{i}] runs layer {source}'s tensors but describes another layer")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind") != "moe":
+                    raise ConfigError(f"layers[{i}].mlp.kind must be 'moe' (or mlp null), got {mlp!r}")
+                for group, keys in (("router", ("experts", "top")), ("expert", ("ff",)), ("shared", ("ff",))):
+                    if not isinstance(mlp.get(group), Mapping):
+                        raise ConfigError(f"layers[{i}].mlp.{group} is missing")
+                    for key in keys:
+                        _require_int(mlp[group].get(key), f"layers[{i}].mlp.{group}.{key}")
+                for group in ("expert", "shared"):
+                    _require_number(mlp[group].get("limit"), f"layers[{i}].mlp.{group}.limit", positive=True)
+                if mlp["router"]["top"] > mlp["router"]["experts"]:
+                    raise ConfigError(f"layers[{i}].mlp.router: top exceeds experts")
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+                "layers": [json.loads(json.dumps(layer)) for layer in self.layers], "norm": dict(self.norm),
+                "residual_mult": self.residual_mult, "logit_scale": self.logit_scale}

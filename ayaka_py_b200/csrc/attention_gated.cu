@@ -1,0 +1,315 @@
+// Attention whose weights are a gate per key instead of a softmax over the keys, over the paged
+// cache, with separate head sizes for keys and values.
+//
+// For the query at absolute position p of a request and the cached positions j <= p of that
+// request: s_j = (q . k_j) * scale, capped as cap * tanh(s_j / cap) when cap > 0, and
+// o = sum_j sigmoid(s_j + bias[head]) v_j.  Nothing is normalized over j, so partial sums over
+// parts of the context simply add.  Scores, weights and sums are 32-bit.
+//
+// ayk_qk_norm_rotary prepares a step's rows from the float32 projection [q | k | v]: the whole
+// query row and the whole key row are RMS-normed (one weight per element), the first rot_dims
+// dimensions of every head are rotated by the position (dimension i with i + rot_dims/2), the
+// queries go to a dense matrix, keys and values into their pages.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ----------------------------------------------------------------- prepare --
+constexpr int MAX_ROT_HALF = 128;
+
+template <typename C>
+__global__ void __launch_bounds__(128)
+qk_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __restrict__ vpages, const float* __restrict__ proj,
+                  long long stride, const float* __restrict__ qw, const float* __restrict__ kw,
+                  const float* __restrict__ freq, int rot_dims, const int* __restrict__ row_req,
+                  const int* __restrict__ positions, const int* __restrict__ table, int table_stride, int page_size,
+                  int H, int G, int D, int Dv, float eps, int writes) {
+  __shared__ float red[8];
+  __shared__ float cs[MAX_ROT_HALF], sn[MAX_ROT_HALF];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int p = positions[t];
+  const int page = table[(size_t)row_req[t] * table_stride + p / page_size];
+  pdl_wait();
+  const float* q = proj + (size_t)t * stride;
+  const float* k = q + (size_t)H * D;
+  const float* v = k + (size_t)G * D;
+  const int nq = H * D, nk = G * D, nv = G * Dv;
+  const int half = rot_dims >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)p * freq[i], &sn[i], &cs[i]);
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) sq = fmaf(q[i], q[i], sq);
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) sk = fmaf(k[i], k[i], sk);
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { red[warp] = sq; red[4 + warp] = sk; }
+  __syncthreads();
+  const float inv_q = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)nq + eps);
+  const float inv_k = 1.0f / sqrtf(((red[4] + red[5]) + (red[6] + red[7])) / (float)nk + eps);
+
+  C* qdst = qout + (size_t)t * nq;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+    const int j = i % D;
+    float val = q[i] * inv_q * qw[i];
+    if (j < half) {
+      const float other = q[i + half] * inv_q * qw[i + half];
+      val = val * cs[j] - other * sn[j];
+    } else if (j < rot_dims) {
+      const float other = q[i - half] * inv_q * qw[i - half];
+      val = val * cs[j - half] + other * sn[j - half];
+    }
+    qdst[i] = from_float<C>(val);
+  }
+  if (!writes || page <= 0) return;
+  const size_t cell = (size_t)page * page_size + (p % page_size);
+  C* kdst = kpages + cell * nk;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int j = i % D;
+    float val = k[i] * inv_k * kw[i];
+    if (j < half) {
+      const float other = k[i + half] * inv_k * kw[i + half];
+      val = val * cs[j] - other * sn[j];
+    } else if (j < rot_dims) {
+      const float other = k[i - half] * inv_k * kw[i - half];
+      val = val * cs[j - half] + other * sn[j - half];
+    }
+    kdst[i] = from_float<C>(val);
+  }
+  C* vdst = vpages + cell * nv;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) vdst[i] = from_float<C>(v[i]);
+}
+
+// ------------------------------------------------------- the general kernel --
+// One block works on up to 32 consecutive rows of one request, one head and one part of the
+// context: 4 warps x 8 rows.  Keys are taken 32 at a time (one per lane for the scores, one
+// value column per lane for the weighted sum).  With several parts a block writes its float32
+// partial sums to scratch and gated_merge_kernel adds the parts in order.
+constexpr int BQ = 32;
+constexpr int BKEYS = 32;
+constexpr int WARPS = 4;
+constexpr int RQ = BQ / WARPS;
+constexpr int MAX_D = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+gated_attention_kernel(T* __restrict__ out, float* __restrict__ partial, const T* __restrict__ q,
+                       const T* __restrict__ kcache, const T* __restrict__ vcache, const int* __restrict__ table,
+                       int table_stride, const int* __restrict__ req_q_start, const int* __restrict__ req_pos0,
+                       int num_req, int total_rows, int H, int Hkv, int D, int Dv, int page_size, float scale,
+                       float cap, const float* __restrict__ head_bias, int part_keys) {
+  pdl_trigger();
+  pdl_wait();
+  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
+  for (int r = 0; r < num_req; ++r) {
+    int len = req_q_start[r + 1] - req_q_start[r];
+    int tiles = (len + BQ - 1) / BQ;
+    if (tile < tiles) { req = r; q0 = tile * BQ; q_len = len; break; }
+    tile -= tiles;
+  }
+  if (req < 0) return;
+  const int h = blockIdx.y, kvh = h / (H / Hkv);
+  const int rows = min(BQ, q_len - q0);
+  const int row0 = req_q_start[req] + q0;
+  const int pos0 = req_pos0[req] + q0;
+  const int last_pos = pos0 + rows - 1;
+  const int part = blockIdx.z;
+  const int k_first = part_keys > 0 ? part * part_keys : 0;
+  const int k_last = part_keys > 0 ? min(last_pos, k_first + part_keys - 1) : last_pos;
+  if (k_first > last_pos) return;                 // the merge does not read parts beyond the context
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ldk = D + 1;
+  const int ldq = (D + 3) & ~3;
+
+  extern __shared__ float smem[];
+  float* Qs = smem;                    // [BQ][ldq]
+  float* Ks = Qs + BQ * ldq;           // [BKEYS][D + 1]
+  float* Vs = Ks + BKEYS * ldk;        // [BKEYS][Dv]
+  float* Ps = Vs + BKEYS * Dv;         // [BQ][BKEYS]
+
+  for (int i = threadIdx.x; i < BQ * D; i += blockDim.x) {
+    int r = i / D, d = i - r * D;
+    Qs[r * ldq + d] = r < rows ? to_float<T>(q[(size_t)(row0 + r) * ((size_t)H * D) + h * D + d]) : 0.f;
+  }
+  const int NC = (Dv + 31) / 32;
+  float acc[RQ][MAX_D / 32];
+#pragma unroll
+  for (int r = 0; r < RQ; ++r)
+#pragma unroll
+    for (int c = 0; c < MAX_D / 32; ++c) acc[r][c] = 0.f;
+  const float bias = head_bias ? head_bias[h] : 0.f;
+  const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+  const int* my_table = table + (size_t)req * table_stride;
+
+  for (int k0 = k_first; k0 <= k_last; k0 += BKEYS) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < BKEYS * D; i += blockDim.x) {
+      int j = i / D, d = i - j * D;
+      int kp = k0 + j;
+      float kv = 0.f;
+      if (kp <= k_last) {
+        int page = my_table[kp / page_size];
+        if (page > 0) kv = to_float<T>(kcache[(((size_t)page * page_size + (kp % page_size)) * Hkv + kvh) * D + d]);
+      }
+      Ks[j * ldk + d] = kv;
+    }
+    for (int i = threadIdx.x; i < BKEYS * Dv; i += blockDim.x) {
+      int j = i / Dv, d = i - j * Dv;
+      int kp = k0 + j;
+      float vv = 0.f;
+      if (kp <= k_last) {
+        int page = my_table[kp / page_size];
+        if (page > 0) vv = to_float<T>(vcache[(((size_t)page * page_size + (kp % page_size)) * Hkv + kvh) * Dv + d]);
+      }
+      Vs[j * Dv + d] = vv;
+    }
+    __syncthreads();
+
+    const int kp = k0 + lane;
+    const bool page_ok = kp <= k_last && my_table[kp / page_size] > 0;
+#pragma unroll
+    for (int r = 0; r < RQ; ++r) {
+      const int row = warp * RQ + r;
+      if (row >= rows) break;
+      const int qpos = pos0 + row;
+      const float* qr = Qs + row * ldq;
+      const float* kr = Ks + lane * ldk;
+      float s = 0.f;
+      int d = 0;
+      for (; d + 4 <= D; d += 4) {
+        float4 qv = *reinterpret_cast<const float4*>(qr + d);
+        s = fmaf(qv.x, kr[d], s);
+        s = fmaf(qv.y, kr[d + 1], s);
+        s = fmaf(qv.z, kr[d + 2], s);
+        s = fmaf(qv.w, kr[d + 3], s);
+      }
+      for (; d < D; ++d) s = fmaf(qr[d], kr[d], s);
+      s *= scale;
+      if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+      Ps[row * BKEYS + lane] = (page_ok && kp <= qpos) ? sigmoidf(s + bias) : 0.f;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < RQ; ++r) {
+      const int row = warp * RQ + r;
+      if (row >= rows) break;
+      const float* pr = Ps + row * BKEYS;
+      for (int j = 0; j < BKEYS; ++j) {
+        float p = pr[j];
+        const float* vr = Vs + j * Dv;
+#pragma unroll
+        for (int c = 0; c < MAX_D / 32; ++c) {
+          int d = lane + 32 * c;
+          if (c < NC && d < Dv) acc[r][c] = fmaf(p, vr[d], acc[r][c]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int r = 0; r < RQ; ++r) {
+    const int row = warp * RQ + r;
+    if (row >= rows) break;
+    const size_t at = (size_t)(row0 + row) * ((size_t)H * Dv) + h * Dv;
+#pragma unroll
+    for (int c = 0; c < MAX_D / 32; ++c) {
+      int d = lane + 32 * c;
+      if (c < NC && d < Dv) {
+        if (part_keys > 0) partial[(size_t)part * total_rows * H * Dv + at + d] = acc[r][c];
+        else out[at + d] = from_float<T>(acc[r][c]);
+      }
+    }
+  }
+}
+
+// out[row] = sum over the parts that hold keys of the row's request, in order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, const int* __restrict__ row_req,
+                   const int* __restrict__ positions, int total_rows, int width, int part_keys) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int used = positions[t] / part_keys + 1;
+  (void)row_req;
+  pdl_wait();
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float s = 0.f;
+    for (int p = 0; p < used; ++p) s += partial[((size_t)p * total_rows + t) * width + i];
+    out[(size_t)t * width + i] = from_float<T>(s);
+  }
+}
+
+}  // namespace
+
+AYK_EXPORT int ayk_qk_norm_rotary(void* qout, void* kpages, void* vpages, const float* proj, long long stride,
+                                  const float* qw, const float* kw, const float* freq, int rot_dims, const int* row_req,
+                                  const int* positions, const int* table, int table_stride, int page_size, int T, int H,
+                                  int G, int D, int Dv, float eps, int writes, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(rot_dims % 2 == 0 && rot_dims <= D && rot_dims / 2 <= MAX_ROT_HALF,
+              "ayk_qk_norm_rotary: %d rotated dimensions do not fit a head of %d (at most %d)", rot_dims, D, 2 * MAX_ROT_HALF);
+  if (dtype == AYK_DTYPE_F32)
+    ayk_launch(qk_prepare_kernel<float>, dim3(T), dim3(128), 0, stream, (float*)qout, (float*)kpages, (float*)vpages, proj,
+               stride, qw, kw, freq, rot_dims, row_req, positions, table, table_stride, page_size, H, G, D, Dv, eps, writes);
+  else if (dtype == AYK_DTYPE_BF16)
+    ayk_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (__nv_bfloat16*)qout, (__nv_bfloat16*)kpages,
+               (__nv_bfloat16*)vpages, proj, stride, qw, kw, freq, rot_dims, row_req, positions, table, table_stride,
+               page_size, H, G, D, Dv, eps, writes);
+  else
+    return ayk_fail("ayk_qk_norm_rotary: unknown dtype %d", dtype);
+  return ayk_check_launch("ayk_qk_norm_rotary");
+}
+
+// q [T, H*D] and out [T, H*Dv] dense, of the cache's dtype.  parts > 1: the context is cut into
+// parts of part_keys keys (grid z) whose partial sums go through ``partial`` [parts, T, H*Dv]
+// float32 and are merged by a second launch; ``positions``: the rows' absolute positions.
+AYK_EXPORT int ayk_gated_attention(void* out, float* partial, const void* q, const void* kcache, const void* vcache,
+                                   const int* table, int table_stride, const int* req_q_start, const int* req_pos0,
+                                   const int* row_req, const int* positions, int num_req, int total_rows, int H, int Hkv,
+                                   int D, int Dv, int page_size, float scale, float cap, const float* head_bias, int parts,
+                                   int part_keys, int dtype, int* launched, cudaStream_t stream) {
+  if (launched) *launched = 0;
+  if (num_req == 0 || total_rows == 0) return 0;
+  AYK_REQUIRE(D >= 1 && D <= MAX_D && Dv >= 1 && Dv <= MAX_D, "ayk_gated_attention: head sizes %d / %d are not in [1, %d]", D, Dv, MAX_D);
+  AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0 && H <= 65535, "ayk_gated_attention: %d heads cannot share %d key/value heads", H, Hkv);
+  AYK_REQUIRE(parts >= 1 && parts <= 65535 && (parts == 1 || (partial && part_keys > 0)), "ayk_gated_attention: bad partition");
+  const int max_tiles = total_rows / BQ + num_req;
+  const size_t smem = ((size_t)BQ * ((D + 3) & ~3) + (size_t)BKEYS * (D + 1) + (size_t)BKEYS * Dv + (size_t)BQ * BKEYS) * sizeof(float);
+  dim3 grid(max_tiles, H, parts);
+  const int pk = parts > 1 ? part_keys : 0;
+  static size_t configured[2] = {0, 0};
+  cudaError_t err;
+  if (dtype == AYK_DTYPE_F32) {
+    if (smem > configured[0]) {
+      err = cudaFuncSetAttribute(gated_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return ayk_fail("ayk_gated_attention: shared memory %zu: %s", smem, cudaGetErrorString(err));
+      configured[0] = smem;
+    }
+    ayk_launch(gated_attention_kernel<float>, grid, dim3(WARPS * 32), smem, stream, (float*)out, partial, (const float*)q,
+               (const float*)kcache, (const float*)vcache, table, table_stride, req_q_start, req_pos0, num_req, total_rows, H,
+               Hkv, D, Dv, page_size, scale, cap, head_bias, pk);
+    if (parts > 1)
+      ayk_launch(gated_merge_kernel<float>, dim3(total_rows), dim3(256), 0, stream, (float*)out, (const float*)partial, row_req,
+                 positions, total_rows, H * Dv, part_keys);
+  } else if (dtype == AYK_DTYPE_BF16) {
+    if (smem > configured[1]) {
+      err = cudaFuncSetAttribute(gated_attention_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return ayk_fail("ayk_gated_attention: shared memory %zu: %s", smem, cudaGetErrorString(err));
+      configured[1] = smem;
+    }
+    ayk_launch(gated_attention_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, stream, (__nv_bfloat16*)out, partial,
+               (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table, table_stride,
+               req_q_start, req_pos0, num_req, total_rows, H, Hkv, D, Dv, page_size, scale, cap, head_bias, pk);
+    if (parts > 1)
+      ayk_launch(gated_merge_kernel<__nv_bfloat16>, dim3(total_rows), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                 (const float*)partial, row_req, positions, total_rows, H * Dv, part_keys);
+  } else {
+    return ayk_fail("ayk_gated_attention: unknown dtype %d", dtype);
+  }
+  if (launched) *launched = parts > 1 ? 2 : 1;
+  return ayk_check_launch("ayk_gated_attention");
+}

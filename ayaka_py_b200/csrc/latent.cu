@@ -29,10 +29,11 @@ __device__ __forceinline__ void turn_pair(float& u, float& v, float angle, float
 
 // ------------------------------------------------------------------ rotary --
 // x[t, head * head_stride + offset + (0 .. dims)) turned in place; x rows lie x_stride apart.
+// ``halves``: dimension i is paired with i + dims/2 instead of neighbours (2i, 2i + 1).
 template <typename T>
 __global__ void rotary_kernel(T* __restrict__ x, long long x_stride, const int* __restrict__ positions,
                               const float* __restrict__ freq, float gain, int heads, int head_stride, int offset,
-                              int dims) {
+                              int dims, int halves) {
   pdl_trigger();
   const float pos = (float)positions[blockIdx.x];
   pdl_wait();
@@ -40,11 +41,13 @@ __global__ void rotary_kernel(T* __restrict__ x, long long x_stride, const int* 
   const int half = dims >> 1;
   for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
     const int h = i / half, p = i - h * half;
-    T* at = row + (size_t)h * head_stride + offset + 2 * p;
-    float u = to_float<T>(at[0]), v = to_float<T>(at[1]);
+    // pairs of neighbours (2p, 2p + 1), or dimension p with p + dims/2
+    T* at = row + (size_t)h * head_stride + offset + (halves ? p : 2 * p);
+    const int gap = halves ? half : 1;
+    float u = to_float<T>(at[0]), v = to_float<T>(at[gap]);
     turn_pair(u, v, pos * freq[p], gain);
     at[0] = from_float<T>(u);
-    at[1] = from_float<T>(v);
+    at[gap] = from_float<T>(v);
   }
 }
 
@@ -400,15 +403,15 @@ int pick_latent_attention(float* out, const float* query, const void* latent_pag
 
 // x[t, head * head_stride + offset + (0 .. dims)) turned in place by positions[t] * freq[i].
 AYK_EXPORT int ayk_rotary(void* x, long long x_stride, const int* positions, const float* freq, float gain, int T,
-                          int heads, int head_stride, int offset, int dims, int dtype, cudaStream_t stream) {
+                          int heads, int head_stride, int offset, int dims, int halves, int dtype, cudaStream_t stream) {
   if (T == 0 || heads == 0 || dims == 0) return 0;
   AYK_REQUIRE(dims % 2 == 0, "ayk_rotary: %d rotated dimensions cannot be paired", dims);
   if (dtype == AYK_DTYPE_F32)
     ayk_launch(rotary_kernel<float>, dim3(T), dim3(128), 0, stream, (float*)x, x_stride, positions, freq, gain, heads,
-               head_stride, offset, dims);
+               head_stride, offset, dims, halves);
   else if (dtype == AYK_DTYPE_BF16)
     ayk_launch(rotary_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (__nv_bfloat16*)x, x_stride, positions, freq,
-               gain, heads, head_stride, offset, dims);
+               gain, heads, head_stride, offset, dims, halves);
   else
     return ayk_fail("ayk_rotary: unknown dtype %d", dtype);
   return ayk_check_launch("ayk_rotary");

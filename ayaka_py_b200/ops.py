@@ -366,9 +366,10 @@ def polynorm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out_dtype: torch.
 
 
 def rotary(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, gain: float, heads: int, head_stride: int,
-           offset: int, dims: int) -> None:
-    """Turns x[t, head * head_stride + offset + (0 .. dims)) in place: neighbouring pairs (2i, 2i+1)
-    by the angle positions[t] * freq[i], cos and sin times ``gain``.  x: rows with unit column stride."""
+           offset: int, dims: int, halves: bool = False) -> None:
+    """Turns x[t, head * head_stride + offset + (0 .. dims)) in place: neighbouring pairs (2i, 2i+1),
+    or with ``halves`` the pairs (i, i + dims/2), by the angle positions[t] * freq[i], cos and sin
+    times ``gain``.  x: rows with unit column stride."""
     lib = _ready()
     if x.dim() != 2 or x.stride(1) != 1:
         raise KernelError("rotary: x must be rows with unit column stride")
@@ -377,7 +378,8 @@ def rotary(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, gain: f
         raise KernelError("rotary: heads, offset and dims do not fit the rows")
     _launch(lib.ayk_rotary(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(_i32(positions, "positions")), _ptr(freq),
                            ctypes.c_float(gain), ctypes.c_int(x.shape[0]), ctypes.c_int(heads), ctypes.c_int(head_stride),
-                           ctypes.c_int(offset), ctypes.c_int(dims), ctypes.c_int(_tag(x.dtype)), _stream()))
+                           ctypes.c_int(offset), ctypes.c_int(dims), ctypes.c_int(1 if halves else 0),
+                           ctypes.c_int(_tag(x.dtype)), _stream()))
 
 
 def latent_prepare(proj: torch.Tensor, latent_pages: torch.Tensor, rope_pages: torch.Tensor, norm_weight: torch.Tensor,
@@ -504,6 +506,235 @@ def hgrn2(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, lower: 
         global launches
         launches += 1
     return out
+
+
+# ------------------- token shift, channel recurrences, gated attention, experts --
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor | None, state: torch.Tensor | None, ctx, out_dtype: torch.dtype) -> torch.Tensor:
+    """x + (previous row - x) * mu per channel; the row before a request's first row is its ``state``
+    [slots, d] float32, which then takes the request's last row.  ``mu`` None: the rows of x in
+    ``out_dtype`` and nothing else."""
+    lib = _ready()
+    _f32(x, "x")
+    T, d = x.shape
+    out = torch.empty((T, d), dtype=out_dtype, device=x.device)
+    if mu is None:
+        _launch(lib.ayk_token_shift(_ptr(out), _ptr(x), _ptr(None), _ptr(None), _ptr(None), _ptr(None), _ptr(None),
+                                    ctypes.c_int(T), ctypes.c_int(d), ctypes.c_int(_tag(out_dtype)), _stream()))
+        return out
+    _f32(mu, "mu"); _f32(state, "state")
+    if mu.numel() != d or state.shape[1:] != (d,):
+        raise KernelError("token_shift: mu [d] and state [slots, d] must fit the rows")
+    _launch(lib.ayk_token_shift(_ptr(out), _ptr(x), _ptr(mu), _ptr(state), _ptr(ctx.row_req), _ptr(ctx.req_q_start),
+                                _ptr(ctx.req_slot), ctypes.c_int(T), ctypes.c_int(d), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, ctx) -> torch.Tensor:
+    """bias + causal convolution over time on every channel of the float32 rows x [T, C] (a column
+    slice of a wider matrix is fine): ``taps`` [n, C] float32, tap-major, the last one multiplies the
+    current row.  ``state`` [slots, n, C] float32: rows 1 .. n - 1 of a slot hold the request's last
+    n - 1 inputs, oldest first (row 0 belongs to the caller), and are brought up to date."""
+    lib = _ready()
+    T, C = x.shape
+    n = taps.shape[0]
+    _f32(taps, "taps"); _f32(state, "state")
+    if x.dtype != torch.float32 or x.stride(1) != 1 or taps.shape[1] != C or state.shape[1:] != (n, C):
+        raise KernelError("causal_conv: x float32 [T, C], taps [n, C] and state [slots, n, C] must fit")
+    if bias is not None:
+        _f32(bias, "bias")
+    out = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    inputs = state[:, 1:] if n > 1 else state                  # the pointer only: rows lie C apart, slots n * C
+    _launch(lib.ayk_causal_conv(_ptr(out), _ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(taps), _ptr(bias),
+                                ctypes.c_void_p(inputs.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.row_req),
+                                _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(T), ctypes.c_int(ctx.num_requests),
+                                ctypes.c_int(C), ctypes.c_int(n), _stream()))
+    if n > 1:
+        global launches
+        launches += 1
+    return out
+
+
+def mingru_scan(proj: torch.Tensor, state: torch.Tensor, ctx, width: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """minGRU over the step's rows, request by request, from and into ``state`` [slots, width] float32.
+    proj: float32 rows [z | u | g] before their sigmoid, candidate and SiLU.  Returns S * silu(g) [T, width]."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(state, "state")
+    T = proj.shape[0]
+    if proj.shape[1] < 3 * width or state.shape[1:] != (width,):
+        raise KernelError("mingru_scan: projection rows or state do not fit")
+    out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+    _launch(lib.ayk_mingru_scan(_ptr(out), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(proj),
+                                ctypes.c_longlong(proj.stride(0)), _ptr(ctx.req_q_start), _ptr(ctx.req_slot),
+                                ctypes.c_int(ctx.num_requests), ctypes.c_int(T), ctypes.c_int(width),
+                                ctypes.c_int(ctx.max_q_len), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def rglru_scan(proj: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, lam: torch.Tensor,
+               state: torch.Tensor, ctx, width: int, blocks: int, decay: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """The real-gated linear recurrent unit over the step's rows: a = exp(-decay sigmoid(r) softplus(lam)),
+    S = a S + sqrt(1 - a^2) sigmoid(i) u, from and into row 0 of ``state`` [slots, n, width] float32.
+    proj: float32 rows whose first ``width`` columns are the other branch before its GELU; u [T, width];
+    gates [T, blocks, r | i] before their biases ``gate_bias`` [blocks, r | i].  Returns S * gelu(y)."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(u, "u"); _f32(gates, "gates"); _f32(gate_bias, "gate_bias"); _f32(lam, "lam"); _f32(state, "state")
+    T = proj.shape[0]
+    if (proj.shape[1] < width or u.shape != (T, width) or gates.numel() != T * 2 * width or gate_bias.numel() != 2 * width
+            or lam.numel() != width or state.shape[2] != width):
+        raise KernelError("rglru_scan: rows, gates or state do not fit")
+    out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+    _launch(lib.ayk_rglru_scan(_ptr(out), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(proj),
+                               ctypes.c_longlong(proj.stride(0)), _ptr(u), _ptr(gates), _ptr(gate_bias), _ptr(lam),
+                               ctypes.c_float(decay), _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(ctx.num_requests),
+                               ctypes.c_int(T), ctypes.c_int(width), ctypes.c_int(blocks), ctypes.c_int(ctx.max_q_len),
+                               ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor, in place (contiguous float32)."""
+    lib = _ready()
+    _f32(x, "x")
+    _launch(lib.ayk_scale(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(factor), _stream()))
+    return x
+
+
+def qk_norm_rotary(proj: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, q_norm: torch.Tensor, k_norm: torch.Tensor,
+                   freq: torch.Tensor, rot_dims: int, ctx, table: torch.Tensor, heads: int, eps: float, writes: bool,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """From float32 projection rows [q | k | v]: the whole query row and the whole key row RMS-normed
+    with one weight per element, the first ``rot_dims`` dimensions of every head rotated by the position
+    (dimension i with i + rot_dims/2); keys and values go into their pages (unless ``writes`` is False),
+    the queries are returned [T, heads * dim] in ``out_dtype``."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(q_norm, "q_norm"); _f32(k_norm, "k_norm"); _f32(freq, "freq")
+    T = proj.shape[0]
+    pages, P, G, D = kpages.shape
+    Dv = vpages.shape[3]
+    if (proj.shape[1] < heads * D + G * D + G * Dv or q_norm.numel() != heads * D or k_norm.numel() != G * D
+            or kpages.dtype != out_dtype or vpages.dtype != out_dtype or not kpages.is_contiguous() or not vpages.is_contiguous()):
+        raise KernelError("qk_norm_rotary: projection rows, weights or pages do not fit")
+    q = torch.empty((T, heads * D), dtype=out_dtype, device=proj.device)
+    _launch(lib.ayk_qk_norm_rotary(_ptr(q), _ptr(kpages), _ptr(vpages), _ptr(proj), ctypes.c_longlong(proj.stride(0)),
+                                   _ptr(q_norm), _ptr(k_norm), _ptr(freq), ctypes.c_int(rot_dims), _ptr(ctx.row_req),
+                                   _ptr(ctx.positions), _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)),
+                                   ctypes.c_int(P), ctypes.c_int(T), ctypes.c_int(heads), ctypes.c_int(G), ctypes.c_int(D),
+                                   ctypes.c_int(Dv), ctypes.c_float(eps), ctypes.c_int(1 if writes else 0),
+                                   ctypes.c_int(_tag(out_dtype)), _stream()))
+    return q
+
+
+GATED_PART = 256          # keys per partition of the context when every request brings one row
+
+
+def sigmoid_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, table: torch.Tensor, ctx, heads: int,
+                      scale: float, softcap: float, head_bias: torch.Tensor | None) -> torch.Tensor:
+    """Causal attention without a softmax over the paged cache: the weight of a visible key is
+    sigmoid(cap tanh(q . k scale / cap) + head_bias[head]) (cap 0: no cap), the output the weighted sum of
+    the values.  q [T, heads * dim] of the pages' dtype; returns [T, heads * vdim].  When every request
+    brings one row the context is cut into partitions whose partial sums are added by a second kernel."""
+    lib = _ready()
+    pages, P, G, D = kpages.shape
+    Dv = vpages.shape[3]
+    T = q.shape[0]
+    if q.shape[1] != heads * D or not q.is_contiguous() or q.dtype != kpages.dtype or vpages.dtype != kpages.dtype:
+        raise KernelError("sigmoid_attention: q must be a contiguous [T, heads * dim] matrix of the pages' dtype")
+    if head_bias is not None:
+        _f32(head_bias, "head_bias")
+    out = torch.empty((T, heads * Dv), dtype=q.dtype, device=q.device)
+    parts, partial = 1, None
+    if ctx.max_q_len == 1:
+        parts = max(1, -(-ctx.cache.max_len // GATED_PART))
+        if parts > 1:
+            partial = _decode_buffer(q.device, parts * T * heads * Dv)
+    launched = ctypes.c_int(0)
+    code = lib.ayk_gated_attention(_ptr(out), _ptr(partial), _ptr(q), _ptr(kpages), _ptr(vpages), _ptr(_i32(table, "table")),
+                                   ctypes.c_int(table.stride(0)), _ptr(ctx.req_q_start), _ptr(ctx.req_pos0), _ptr(ctx.row_req),
+                                   _ptr(ctx.positions), ctypes.c_int(ctx.num_requests), ctypes.c_int(T), ctypes.c_int(heads),
+                                   ctypes.c_int(G), ctypes.c_int(D), ctypes.c_int(Dv), ctypes.c_int(P), ctypes.c_float(scale),
+                                   ctypes.c_float(softcap), _ptr(head_bias), ctypes.c_int(parts), ctypes.c_int(GATED_PART),
+                                   ctypes.c_int(_tag(q.dtype)), ctypes.byref(launched), _stream())
+    global launches
+    launches += launched.value
+    _check(code)
+    return out
+
+
+class MoeRoute:
+    """A step's routing on the device: ``ids`` and ``weights`` [T, top]; ``sorted`` [T * top], the
+    (token, choice) pairs laid out expert by expert; ``tiles``: the number of row tiles and for each its
+    expert, first sorted row and rows."""
+
+    def __init__(self, ids, weights, sorted_pairs, tiles, max_tiles, top):
+        self.ids, self.weights, self.sorted, self.tiles, self.max_tiles, self.top = ids, weights, sorted_pairs, tiles, max_tiles, top
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int) -> MoeRoute:
+    """The ``top`` largest of each row's first ``experts`` float32 logits, weighted by the softmax over
+    the chosen ones, and the plan of the grouped products."""
+    lib = _ready()
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[1] < experts:
+        raise KernelError("moe_route: logits must be float32 rows of at least ``experts`` columns")
+    T = logits.shape[0]
+    rows = int(lib.ayk_moe_tile_rows())
+    max_tiles = (T * top) // rows + experts
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    sorted_pairs = torch.empty((T * top,), dtype=torch.int32, device=logits.device)
+    tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=logits.device)
+    _launch(lib.ayk_moe_route(_ptr(ids), _ptr(weights), _ptr(sorted_pairs), _ptr(tiles), _ptr(logits),
+                              ctypes.c_longlong(logits.stride(0)), ctypes.c_int(T), ctypes.c_int(experts), ctypes.c_int(top), _stream()))
+    global launches
+    launches += 1
+    return MoeRoute(ids, weights, sorted_pairs, tiles, max_tiles, top)
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | None, out_dtype: torch.dtype) -> torch.Tensor:
+    """Grouped product over the sorted pairs.  ``glu`` = (limit, slope): a holds the tokens' rows
+    [T, K], w [experts, 2 N, K] gate over up, and the result is the experts' activation
+    min(g, limit) sigmoid(slope g) (clamp(u) + 1) per sorted pair, [T * top, N] in ``out_dtype``.  ``glu`` None:
+    a holds rows per sorted pair, w [experts, N, K], and the float32 result [T * top, N] lies pair by pair
+    (token-major).  bfloat16 operands run on the tensor cores, float32 on the FP32 pipes."""
+    lib = _ready()
+    E, n_w, K = w.shape
+    if a.dtype != w.dtype or a.shape[1] != K or a.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError("moe_gemm: operands do not fit")
+    pairs = route.sorted.numel()
+    N = n_w // 2 if glu is not None else n_w
+    out = torch.empty((pairs, N), dtype=out_dtype, device=a.device)
+    limit, slope = glu if glu is not None else (0.0, 0.0)
+    _launch(lib.ayk_moe_gemm(_ptr(out), _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), _ptr(route.sorted), _ptr(route.tiles),
+                             ctypes.c_int(route.max_tiles), ctypes.c_int(route.top), ctypes.c_int(1 if glu is not None else 0),
+                             ctypes.c_int(0 if glu is not None else 1), ctypes.c_int(N), ctypes.c_int(n_w), ctypes.c_int(K),
+                             ctypes.c_int(1 if glu is not None else 0), ctypes.c_float(limit), ctypes.c_float(slope),
+                             ctypes.c_int(_tag(a.dtype)), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def glu_limited(x: torch.Tensor, n: int, limit: float, slope: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """min(g, limit) sigmoid(slope g) (clamp(u, -limit, limit) + 1) with g = x[:, :n] and u = x[:, n:2n]
+    of float32 rows."""
+    lib = _ready()
+    if x.dtype != torch.float32 or x.stride(1) != 1 or x.shape[1] < 2 * n:
+        raise KernelError("glu_limited: float32 rows of at least 2 n columns")
+    out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
+    _launch(lib.ayk_glu_limited(_ptr(out), _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_int(x.shape[0]), ctypes.c_int(n),
+                                ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def moe_combine(picked: torch.Tensor, route: MoeRoute, shared: torch.Tensor, mix: torch.Tensor | None) -> torch.Tensor:
+    """shared[t] = sum_k weights[t, k] picked[t * top + k] + sigmoid(mix[t]) shared[t], in place; float32."""
+    lib = _ready()
+    _f32(picked, "picked"); _f32(shared, "shared")
+    T, d = shared.shape
+    if picked.shape != (T * route.top, d) or (mix is not None and (mix.dtype != torch.float32 or mix.numel() != T)):
+        raise KernelError("moe_combine: rows do not fit")
+    _launch(lib.ayk_moe_combine(_ptr(shared), _ptr(picked), _ptr(route.weights), _ptr(mix),
+                                ctypes.c_longlong(mix.stride(0) if mix is not None else 0), ctypes.c_int(T),
+                                ctypes.c_int(route.top), ctypes.c_int(d), _stream()))
+    return shared
 
 
 # ------------------------------------------------------------- dispatchers --

@@ -55,3 +55,32 @@ class SandwichMixerBlock(SandwichBlock):
 register_block(PreNormBlock.KIND, PreNormBlock)
 register_block(SandwichBlock.KIND, SandwichBlock)
 register_block(SandwichMixerBlock.KIND, SandwichMixerBlock)
+
+
+class PostNormBlock(Block):
+    """The sublayers read the residual stream itself and only their outputs are normed:
+    x += norm1(mixer(shift(x))); x += norm2(ffn(x)).  ``shift`` blends every channel of the
+    mixer's input with the previous token's (``TokenShift``); it also brings the stream into the
+    compute dtype, which a plain conversion does for the feed-forward.  The closing norms carry
+    the residual multiplier and add to the stream themselves (``RMSNorm.add_normed``)."""
+
+    KIND = "post_norm"
+    PARTS = ("shift", "mixer", "norm1", "ffn", "norm2")
+
+    def forward(self, x, ctx, caches):
+        h = self.shift.forward(x, ctx, caches["shift"])
+        x = self.norm1.add_normed(x, self.mixer.forward(h, None, ctx, caches.get("mixer")))
+        if "ffn" in self.parts:
+            x = self.norm2.add_normed(x, self.ffn.forward(self.shift.convert(x), None, ctx))
+        return x
+
+
+class PostNormMixerBlock(PostNormBlock):
+    """The same without a feed-forward."""
+
+    KIND = "post_norm_mixer_only"
+    PARTS = ("shift", "mixer", "norm1")
+
+
+register_block(PostNormBlock.KIND, PostNormBlock)
+register_block(PostNormMixerBlock.KIND, PostNormMixerBlock)

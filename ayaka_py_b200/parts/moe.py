@@ -1,0 +1,86 @@
+"""Mixture of experts with a gated shared expert.
+
+Router: z = W_r h in 32-bit; the ``top`` experts with the largest z are chosen and weighted by
+the softmax over the chosen z only.  An expert (no biases): g = min(W_gate h, limit),
+u = clamp(W_up h, -limit, limit), y = W_down (g sigmoid(1.702 g) (u + 1)).  The output is the
+weighted sum of the chosen experts' y plus the shared expert's (same form, sizes and limit of
+its own), which runs for every token and is multiplied by sigmoid(w_mix . h), one number per
+token.
+
+The experts' matrices are kept stacked ([experts, 2 inner, width] with gate over up, and
+[experts, width, inner]); a step sorts its (token, choice) pairs by expert on the device and runs
+two grouped products over the sorted rows, so nothing about the routing comes back to the host
+(``csrc/moe.cu``).  The shared expert's gate, up and mixing row are one dense product."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorDecl, register_part
+
+
+def _padded(n: int) -> int:
+    return -(-n // 8) * 8
+
+
+class MoE(FeedForward):
+    KIND = "moe"
+    GATE_SLOPE = 1.702
+
+    def __init__(self, width: int, experts: int, top: int, inner: int, limit: float, shared_inner: int,
+                 shared_limit: float, dtype=torch.float32, device="cuda"):
+        if not 1 <= top <= min(experts, 8):
+            raise ValueError(f"top {top} of {experts} experts: the routing kernel picks 1 to 8")
+        self.width, self.experts, self.top, self.inner, self.limit = width, experts, top, inner, float(limit)
+        self.shared_inner, self.shared_limit, self.dtype = shared_inner, float(shared_limit), dtype
+
+    def tensors(self):
+        d, ff, sf = self.width, self.inner, self.shared_inner
+        out = {"router_weight": TensorDecl((self.experts, d), "matrix"),
+               "shared_gate": TensorDecl((sf, d), "matrix"), "shared_up": TensorDecl((sf, d), "matrix"),
+               "shared_down": TensorDecl((d, sf), "matrix"), "shared_mix": TensorDecl((1, d), "matrix")}
+        for e in range(self.experts):
+            out[f"gate_{e}"] = TensorDecl((ff, d), "matrix")
+            out[f"up_{e}"] = TensorDecl((ff, d), "matrix")
+            out[f"down_{e}"] = TensorDecl((d, ff), "matrix")
+        return out
+
+    def bind(self, tensors):
+        E, d, ff, sf = self.experts, self.width, self.inner, self.shared_inner
+        first = tensors["gate_0"]
+        self.in_weight = torch.empty((E, 2 * ff, d), dtype=first.dtype, device=first.device)
+        self.down_weight = torch.empty((E, d, ff), dtype=first.dtype, device=first.device)
+        for e in range(E):
+            self.in_weight[e, :ff], self.in_weight[e, ff:] = tensors[f"gate_{e}"], tensors[f"up_{e}"]
+            self.down_weight[e] = tensors[f"down_{e}"]
+        rows = _padded(max(E, 8))
+        self.router_weight = torch.zeros((rows, d), dtype=first.dtype, device=first.device)
+        self.router_weight[:E] = tensors["router_weight"]
+        self.shared_in = torch.zeros((_padded(2 * sf + 1), d), dtype=first.dtype, device=first.device)
+        self.shared_in[:sf], self.shared_in[sf:2 * sf], self.shared_in[2 * sf] = tensors["shared_gate"], tensors["shared_up"], tensors["shared_mix"][0]
+        self.shared_down = tensors["shared_down"]
+        for e in range(E):                         # per-expert views, as the loader's bookkeeping expects attributes
+            setattr(self, f"gate_{e}", self.in_weight[e, :ff])
+            setattr(self, f"up_{e}", self.in_weight[e, ff:])
+            setattr(self, f"down_{e}", self.down_weight[e])
+        self.shared_gate, self.shared_up, self.shared_mix = self.shared_in[:sf], self.shared_in[sf:2 * sf], self.shared_in[2 * sf:2 * sf + 1]
+
+    def forward(self, h, residual, ctx):
+        """ff(h) (+ residual), float32 [T, width].  h: rows in the compute dtype."""
+        T, d, K = h.shape[0], self.width, self.top
+        logits = ops.linear(h, self.router_weight, None, out_dtype=torch.float32)
+        route = ops.moe_route(logits, self.experts, K)
+        hidden = ops.moe_gemm(h, self.in_weight, route, glu=(self.limit, self.GATE_SLOPE), out_dtype=self.dtype)
+        picked = ops.moe_gemm(hidden, self.down_weight, route, glu=None, out_dtype=torch.float32)          # [T * K, d]
+        sp = ops.linear(h, self.shared_in, None, out_dtype=torch.float32)
+        sh = ops.glu_limited(sp, self.shared_inner, self.shared_limit, self.GATE_SLOPE, self.dtype)
+        shared = ops.linear(sh, self.shared_down, None, out_dtype=torch.float32)
+        out = ops.moe_combine(picked, route, shared, sp[:, 2 * self.shared_inner])
+        if residual is not None:
+            residual.add_(out)
+            return residual
+        return out
+
+
+register_part(MoE.KIND, MoE)

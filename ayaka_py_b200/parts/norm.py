@@ -33,17 +33,25 @@ class LayerNorm(Norm):
 class RMSNorm(Norm):
     """x / sqrt(mean(x^2) + eps) * weight, eps inside the root, all in 32-bit.  ``out_scale`` is a
     constant factor on the result: a norm that closes a sublayer carries the residual multiplier
-    there, and ``add_normed`` adds its scaled output to the residual stream in one kernel."""
+    there, and ``add_normed`` adds its scaled output to the residual stream in one kernel.
+    ``offset``: the checkpoint stores weight - offset (a weight kept around zero has offset 1); the
+    sum is made once, in 32-bit, when the tensor is bound."""
 
     KIND = "rmsnorm"
 
-    def __init__(self, width: int, eps: float, out_scale: float = 1.0, dtype=torch.float32, device="cuda"):
-        self.width, self.eps, self.out_scale = width, float(eps), float(out_scale)
+    def __init__(self, width: int, eps: float, out_scale: float = 1.0, offset: float = 0.0,
+                 dtype=torch.float32, device="cuda"):
+        self.width, self.eps, self.out_scale, self.offset = width, float(eps), float(out_scale), float(offset)
         self.dtype = dtype
         self.weight = None
 
     def tensors(self):
         return {"weight": TensorDecl((self.width,), "vector")}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        if self.offset != 0.0:
+            self.weight = self.weight + self.offset          # a tensor of the part's own: the stored one may be shared
 
     def forward(self, x, ctx, rows=None):
         if self.out_scale != 1.0:

@@ -46,14 +46,19 @@ class Rotary(PositionEncoding):
     and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency becomes
     f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1.
     Frequencies are computed once on the host in double precision and kept as float32; angles,
-    cos and sin are 32-bit on the device.  No tensors of its own."""
+    cos and sin are 32-bit on the device.  ``layout`` "halves" pairs dimension i with i + dims/2
+    instead (the same frequencies).  No tensors of its own."""
 
     KIND = "rotary"
 
-    def __init__(self, dims: int, base: float, scaling: dict | None = None, dtype=torch.float32, device="cuda"):
+    def __init__(self, dims: int, base: float, scaling: dict | None = None, layout: str = "interleaved",
+                 dtype=torch.float32, device="cuda"):
         if dims < 2 or dims % 2:
             raise ValueError(f"rotary positions pair dimensions: dims must be even and positive, got {dims}")
+        if layout not in ("interleaved", "halves"):
+            raise ValueError(f"rotary layout {layout!r}: 'interleaved' or 'halves'")
         self.dims, self.base, self.scaling = dims, float(base), dict(scaling) if scaling else None
+        self.halves = layout == "halves"
         freq, self.gain = rotary_frequencies(dims, self.base, self.scaling)
         self.freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32)
         if device != "meta":
@@ -61,7 +66,7 @@ class Rotary(PositionEncoding):
 
     def rotate(self, x, positions, heads: int, head_stride: int, offset: int = 0) -> None:
         """Turns x[t, head * head_stride + offset + (0 .. dims)) in place."""
-        ops.rotary(x, positions, self.freq, self.gain, heads, head_stride, offset, self.dims)
+        ops.rotary(x, positions, self.freq, self.gain, heads, head_stride, offset, self.dims, self.halves)
 
     def rotate_qk(self, q, k, heads, kv_heads, head_dim, ctx) -> None:
         self.rotate(q, ctx.positions, heads, head_dim)
