@@ -226,6 +226,201 @@ gated_attention_kernel(T* __restrict__ out, float* __restrict__ partial, const T
   }
 }
 
+// ------------------------------------------------- the tensor-core kernel --
+// bfloat16, head sizes in multiples of 16 up to 128.  The rows of a tile are (token, query head of
+// one key/value head) pairs, token-major: a block of four warps holds 64 of them (16 per warp), so the
+// query heads that share a key/value head also share its loads, in prompts and in single-token steps
+// alike.  Keys come 64 at a time through shared memory.  S = Q K^T with mma.sync m16n8k16 (float32
+// sums); the weights are computed in 32-bit in the registers of S's fragments and enter the second
+// product as two bfloat16 parts (the value and what its rounding left), so that the sum over the keys
+// sees 32-bit weights; O stays in registers.
+constexpr int TC_ROWS = 64, TC_KEYS = 64, TC_MAX_D = 128;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// weight of a key: sigmoid(cap * tanh(s * scale / cap) + bias), tanh(x) = 1 - 2 / (exp(2x) + 1)
+__device__ __forceinline__ float gate_weight(float s, float scale, float cap, float two_over_cap, float bias) {
+  s *= scale;
+  if (cap > 0.f) s = cap * (1.0f - __fdividef(2.0f, __expf(s * two_over_cap) + 1.0f));
+  return __fdividef(1.0f, 1.0f + __expf(-(s + bias)));
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                           const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
+                           const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ table, int table_stride,
+                           const int* __restrict__ req_q_start, const int* __restrict__ req_pos0, int num_req,
+                           int total_rows, int H, int Hkv, int page_size, float scale, float cap,
+                           const float* __restrict__ head_bias, int part_keys, int tq) {
+  constexpr int LDK = D + 8, LDV = DV + 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [TC_KEYS][LDK]; the queries pass through here first
+  __nv_bfloat16* Vs = Ks + TC_KEYS * LDK;                             // [TC_KEYS][LDV]
+  pdl_trigger();
+  pdl_wait();
+  const int hpg = H / Hkv;
+  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
+  for (int r = 0; r < num_req; ++r) {
+    int len = req_q_start[r + 1] - req_q_start[r];
+    int tiles = (len + tq - 1) / tq;
+    if (tile < tiles) { req = r; q0 = tile * tq; q_len = len; break; }
+    tile -= tiles;
+  }
+  if (req < 0) return;
+  const int g = blockIdx.y;
+  const int tokens = min(tq, q_len - q0);
+  const int rows = tokens * hpg;                    // live rows of the tile, <= 64
+  const int row0 = req_q_start[req] + q0;
+  const int pos0 = req_pos0[req] + q0;
+  const int last_pos = pos0 + tokens - 1;
+  const int part = blockIdx.z;
+  const int k_first = part_keys > 0 ? part * part_keys : 0;
+  const int k_last = part_keys > 0 ? min(last_pos, k_first + part_keys - 1) : last_pos;
+  if (k_first > last_pos) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+  const int* my_table = table + (size_t)req * table_stride;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+  // queries -> shared memory -> A fragments of this warp's 16 rows
+  for (int i = tid; i < TC_ROWS * (D / 8); i += 128) {
+    const int m = i / (D / 8), piece = i - m * (D / 8);
+    uint4 v = zero4;
+    if (m < rows) {
+      const int tok = m / hpg, head = g * hpg + (m - tok * hpg);
+      v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + tok) * H + head) * D + piece * 8);
+    }
+    *reinterpret_cast<uint4*>(Ks + m * LDK + piece * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const __nv_bfloat16* base = Ks + (warp * 16 + gid) * LDK + ks * 16 + tig * 2;
+    qf[ks][0] = *reinterpret_cast<const uint32_t*>(base);
+    qf[ks][1] = *reinterpret_cast<const uint32_t*>(base + 8 * LDK);
+    qf[ks][2] = *reinterpret_cast<const uint32_t*>(base + 8);
+    qf[ks][3] = *reinterpret_cast<const uint32_t*>(base + 8 * LDK + 8);
+  }
+  // this thread's two rows: their positions and their heads' biases
+  int qpos[2];
+  float bias[2];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = warp * 16 + gid + half * 8;
+    const int tok = m / hpg;
+    qpos[half] = m < rows ? pos0 + tok : -1;                       // a dead row sees nothing
+    bias[half] = (head_bias && m < rows) ? head_bias[g * hpg + (m - tok * hpg)] : 0.f;
+  }
+  float o[DV / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
+  const float two_over_cap = cap > 0.f ? 2.0f / cap : 0.f;
+
+  for (int k0 = k_first; k0 <= k_last; k0 += TC_KEYS) {
+    __syncthreads();                                   // the fragments of the tile before (or the queries) are read
+    for (int i = tid; i < TC_KEYS * (D / 8); i += 128) {
+      const int j = i / (D / 8), piece = i - j * (D / 8);
+      const int kp = k0 + j;
+      uint4 v = zero4;
+      if (kp <= k_last) {
+        const int page = my_table[kp / page_size];
+        if (page > 0) v = *reinterpret_cast<const uint4*>(kcache + (((size_t)page * page_size + (kp % page_size)) * Hkv + g) * D + piece * 8);
+      }
+      *reinterpret_cast<uint4*>(Ks + j * LDK + piece * 8) = v;
+    }
+    for (int i = tid; i < TC_KEYS * (DV / 8); i += 128) {
+      const int j = i / (DV / 8), piece = i - j * (DV / 8);
+      const int kp = k0 + j;
+      uint4 v = zero4;
+      if (kp <= k_last) {
+        const int page = my_table[kp / page_size];
+        if (page > 0) v = *reinterpret_cast<const uint4*>(vcache + (((size_t)page * page_size + (kp % page_size)) * Hkv + g) * DV + piece * 8);
+      }
+      *reinterpret_cast<uint4*>(Vs + j * LDV + piece * 8) = v;
+    }
+    __syncthreads();
+    if (warp * 16 >= rows) continue;                   // a warp without live rows only helps with the loads
+
+    // S = Q K^T: 8 tiles of 8 keys
+    float sc[TC_KEYS / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < TC_KEYS / 8; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sc[nt][c] = 0.f;
+      const __nv_bfloat16* kb = Ks + (nt * 8 + gid) * LDK + tig * 2;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        mma_bf16(sc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kb + ks * 16), *reinterpret_cast<const uint32_t*>(kb + ks * 16 + 8));
+    }
+    // weights, in place; fragment element c of tile nt: row gid + 8 (c / 2), key k0 + 8 nt + 2 tig + (c & 1)
+    const bool edge = k0 + TC_KEYS - 1 > pos0 || k0 + TC_KEYS - 1 > k_last;
+#pragma unroll
+    for (int nt = 0; nt < TC_KEYS / 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = k0 + nt * 8 + tig * 2 + (c & 1);
+        const float w = gate_weight(sc[nt][c], scale, cap, two_over_cap, bias[c >> 1]);
+        sc[nt][c] = (edge && (key > qpos[c >> 1] || key > k_last)) || qpos[c >> 1] < 0 ? 0.f : w;
+      }
+    // O += P V, P as two bfloat16 parts
+#pragma unroll
+    for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float a = sc[2 * ks + (r >> 1)][(r & 1) * 2], b = sc[2 * ks + (r >> 1)][(r & 1) * 2 + 1];
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+        hi[r] = *reinterpret_cast<const uint32_t*>(&h2);
+        lo[r] = pack_bf16(a - __low2float(h2), b - __high2float(h2));
+      }
+#pragma unroll
+      for (int np = 0; np < DV / 16; ++np) {
+        // two value tiles (16 columns) at a time: four 8x8 matrices, transposed on the way in
+        uint32_t b0, b1, b2, b3;
+        const __nv_bfloat16* at = Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + np * 16 + (lane >> 4) * 8;
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(at);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+        mma_bf16(o[2 * np], hi, b0, b1);
+        mma_bf16(o[2 * np], lo, b0, b1);
+        mma_bf16(o[2 * np + 1], hi, b2, b3);
+        mma_bf16(o[2 * np + 1], lo, b2, b3);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = warp * 16 + gid + half * 8;
+    if (m >= rows) continue;
+    const int tok = m / hpg, head = g * hpg + (m - tok * hpg);
+    const size_t at = ((size_t)(row0 + tok) * H + head) * DV;
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+      const int col = nt * 8 + tig * 2;
+      if (part_keys > 0) {
+        float* dst = partial + (size_t)part * total_rows * H * DV + at + col;
+        dst[0] = o[nt][half * 2];
+        dst[1] = o[nt][half * 2 + 1];
+      } else {
+        *reinterpret_cast<__nv_bfloat162*>(out + at + col) = __floats2bfloat162_rn(o[nt][half * 2], o[nt][half * 2 + 1]);
+      }
+    }
+  }
+}
+
 // out[row] = sum over the parts that hold keys of the row's request, in order.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -264,6 +459,10 @@ AYK_EXPORT int ayk_qk_norm_rotary(void* qout, void* kpages, void* vpages, const 
   return ayk_check_launch("ayk_qk_norm_rotary");
 }
 
+static int g_tensor_cores = 1;
+// 0: bfloat16 steps run on the FP32 pipes too (for comparing the two kernels).
+AYK_EXPORT void ayk_gated_attention_tensor_cores(int on) { g_tensor_cores = on ? 1 : 0; }
+
 // q [T, H*D] and out [T, H*Dv] dense, of the cache's dtype.  parts > 1: the context is cut into
 // parts of part_keys keys (grid z) whose partial sums go through ``partial`` [parts, T, H*Dv]
 // float32 and are merged by a second launch; ``positions``: the rows' absolute positions.
@@ -277,10 +476,32 @@ AYK_EXPORT int ayk_gated_attention(void* out, float* partial, const void* q, con
   AYK_REQUIRE(D >= 1 && D <= MAX_D && Dv >= 1 && Dv <= MAX_D, "ayk_gated_attention: head sizes %d / %d are not in [1, %d]", D, Dv, MAX_D);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0 && H <= 65535, "ayk_gated_attention: %d heads cannot share %d key/value heads", H, Hkv);
   AYK_REQUIRE(parts >= 1 && parts <= 65535 && (parts == 1 || (partial && part_keys > 0)), "ayk_gated_attention: bad partition");
+  const int pk = parts > 1 ? part_keys : 0;
+  // bfloat16 with head sizes that the tensor-core kernel holds
+  const int hpg = H / Hkv;
+  if (dtype == AYK_DTYPE_BF16 && g_tensor_cores && hpg <= TC_ROWS && ((D == 64 && Dv == 64) || (D == 128 && Dv == 128) ||
+                                                                     (D == 64 && Dv == 128) || (D == 128 && Dv == 64) ||
+                                                                     (D == 32 && Dv == 32) || (D == 16 && Dv == 16))) {
+    const int tq = TC_ROWS / hpg;
+    dim3 grid(total_rows / tq + num_req, Hkv, parts);
+#define AYK_GATED(DD, DDV)                                                                                                  \
+  if (D == DD && Dv == DDV) {                                                                                               \
+    const size_t smem = (size_t)TC_KEYS * (DD + 8 + DDV + 8) * sizeof(__nv_bfloat16);                                       \
+    ayk_launch(gated_attention_mma_kernel<DD, DDV>, grid, dim3(128), smem, stream, (__nv_bfloat16*)out, partial,            \
+               (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table, table_stride,    \
+               req_q_start, req_pos0, num_req, total_rows, H, Hkv, page_size, scale, cap, head_bias, pk, tq);               \
+  }
+    AYK_GATED(64, 64) AYK_GATED(128, 128) AYK_GATED(64, 128) AYK_GATED(128, 64) AYK_GATED(32, 32) AYK_GATED(16, 16)
+#undef AYK_GATED
+    if (parts > 1)
+      ayk_launch(gated_merge_kernel<__nv_bfloat16>, dim3(total_rows), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                 (const float*)partial, row_req, positions, total_rows, H * Dv, part_keys);
+    if (launched) *launched = parts > 1 ? 2 : 1;
+    return ayk_check_launch("ayk_gated_attention");
+  }
   const int max_tiles = total_rows / BQ + num_req;
   const size_t smem = ((size_t)BQ * ((D + 3) & ~3) + (size_t)BKEYS * (D + 1) + (size_t)BKEYS * Dv + (size_t)BQ * BKEYS) * sizeof(float);
   dim3 grid(max_tiles, H, parts);
-  const int pk = parts > 1 ? part_keys : 0;
   static size_t configured[2] = {0, 0};
   cudaError_t err;
   if (dtype == AYK_DTYPE_F32) {

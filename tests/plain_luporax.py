@@ -134,9 +134,14 @@ def expert(h, t, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ t[p + "down"].T
 
 
-def moe(h, t, p, mlp):
+def moe(h, t, p, mlp, margins=None):
+    """``margins``: a list that receives, per row, how far the last chosen logit lies above the first one
+    left out, as a fraction of the row's largest logit (a small value: rounding may turn the choice)."""
     E, K = mlp["router"]["experts"], mlp["router"]["top"]
     logits = h @ t[p + "router"].T
+    if margins is not None and K < E:
+        ranked = -np.sort(-logits, axis=1)
+        margins.append((ranked[:, K - 1] - ranked[:, K]) / np.abs(logits).max(axis=1))
     out = np.zeros_like(h)
     for i in range(h.shape[0]):
         order = np.argsort(-logits[i], kind="stable")[:K]
@@ -150,9 +155,9 @@ def moe(h, t, p, mlp):
 
 # --------------------------------------------------------------------- model --
 
-def forward(cfg, t, tokens, layers_out=None):
+def forward(cfg, t, tokens, layers_out=None, margins=None):
     """Logits [T, vocab] of one sequence from position 0.  ``layers_out``: a list that
-    receives the residual stream after every layer run."""
+    receives the residual stream after every layer run; ``margins``: see ``moe``."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x = t["embed"][np.asarray(tokens)]
     for i, layer in enumerate(cfg["layers"]):
@@ -164,7 +169,7 @@ def forward(cfg, t, tokens, layers_out=None):
             y = MIXERS[layer["type"]](h, t, p + "mix.", layer["mixer"])
         x = x + m * norm_one_plus(y, t[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + m * norm_one_plus(moe(x, t, p + "mlp.", layer["mlp"]), t[p + "norm2"], eps)
+            x = x + m * norm_one_plus(moe(x, t, p + "mlp.", layer["mlp"], margins), t[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.copy())
     return (norm_one_plus(x, t["final.norm"], eps) @ t["embed"].T) * cfg["logit_scale"]
@@ -269,3 +274,13 @@ def write_folder(folder, cfg, tensors):
     (folder / "config.json").write_text(json.dumps(cfg, indent=1))
     write_safetensors(folder / "model.safetensors", tensors)
     return folder
+
+
+def greedy_generate(cfg, t, prompt, n):
+    """n tokens, each the arg max of the last position's logits (the whole sequence is run again every time)."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(np.argmax(forward(cfg, t, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
