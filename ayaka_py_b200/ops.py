@@ -629,12 +629,15 @@ GATED_PART = 256          # keys per partition of the context when every request
 
 
 def sigmoid_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, table: torch.Tensor, ctx, heads: int,
-                      scale: float, softcap: float, head_bias: torch.Tensor | None) -> torch.Tensor:
+                      scale: float, softcap: float, head_bias: torch.Tensor | None, tensor_cores: bool = True) -> torch.Tensor:
     """Causal attention without a softmax over the paged cache: the weight of a visible key is
     sigmoid(cap tanh(q . k scale / cap) + head_bias[head]) (cap 0: no cap), the output the weighted sum of
     the values.  q [T, heads * dim] of the pages' dtype; returns [T, heads * vdim].  When every request
-    brings one row the context is cut into partitions whose partial sums are added by a second kernel."""
+    brings one row the context is cut into partitions whose partial sums are added by a second kernel.
+    bfloat16 pages with head sizes of 16, 32, 64 or 128 go through the tensor-core kernel (``tensor_cores``
+    False: through the kernel on the FP32 pipes like everything else)."""
     lib = _ready()
+    lib.ayk_gated_attention_tensor_cores(ctypes.c_int(1 if tensor_cores else 0))
     pages, P, G, D = kpages.shape
     Dv = vpages.shape[3]
     T = q.shape[0]

@@ -442,6 +442,34 @@ def test_mixture_of_experts_alone(dtype, d, E, top, ff, sff):
     assert np.abs(host(got) - (base + want)).max() < tol(dtype, 3 * float(np.abs(want).max()))
 
 
+# ------------------------------------------------- the faster kernels against the plain ones --
+
+@pytest.mark.parametrize("H,G,D,Dv,P", [(8, 1, 64, 64, 16), (6, 2, 64, 64, 16), (4, 4, 128, 128, 16), (3, 1, 64, 128, 8),
+                                        (2, 2, 128, 64, 32), (5, 5, 32, 32, 16), (4, 2, 16, 16, 16)])
+def test_tensor_core_sigmoid_attention_against_the_32_bit_pipes(H, G, D, Dv, P):
+    """Prompts, portions on top of a cached context, single rows (whose context is cut into partitions
+    and added up), all in one cache: both kernels read the same pages."""
+    from ayaka_py_b200 import ops
+    from ayaka_py_b200.cache import CacheGroupSpec
+    from ayaka_py_b200.parts import KVNeed
+    cache, runner = context_for([CacheGroupSpec("g", KVNeed(G, D, None, G, Dv), 1)], "bfloat16", max_requests=4,
+                                page_size=P, pages=2048 // P, positions=1024)
+    kp, vp = cache.kv_layer(0, 0)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    kp.copy_(torch.randn(kp.shape, generator=gen, device="cuda"))
+    vp.copy_(torch.randn(vp.shape, generator=gen, device="cuda"))
+    bias = torch.linspace(-3.0, -1.0, H, device="cuda")
+    for plan in ({0: 500, 1: 33, 2: 1}, {0: 7, 2: 130}, {0: 1, 1: 1, 2: 1}, {1: 1}, {0: 64, 1: 1, 2: 1, 3: 17}, {3: 300}):
+        ctx, res = step_of(cache, runner, plan)
+        q = (torch.randn(ctx.num_rows, H * D, generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+        for cap in (0.0, 3.0):
+            a = ops.sigmoid_attention(q, kp, vp, ctx.tables[0], ctx, H, 0.2, cap, bias, tensor_cores=False)
+            b = ops.sigmoid_attention(q, kp, vp, ctx.tables[0], ctx, H, 0.2, cap, bias, tensor_cores=True)
+            assert not torch.isnan(b.float()).any()
+            assert float((a.float() - b.float()).abs().max()) < 0.01 * float(a.float().abs().max()) + 1e-3, (plan, cap)
+        cache.commit(res)
+
+
 # --------------------------------------------------------------- whole models --
 
 def test_layers_one_by_one_in_32_bit(models):
