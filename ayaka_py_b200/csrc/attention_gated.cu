@@ -232,9 +232,8 @@ gated_attention_kernel(T* __restrict__ out, float* __restrict__ partial, const T
 // query heads that share a key/value head also share its loads, in prompts and in single-token steps
 // alike.  Keys come 64 at a time through shared memory.  S = Q K^T with mma.sync m16n8k16 (float32
 // sums); the weights are computed in 32-bit in the registers of S's fragments and enter the second
-// product as two bfloat16 parts (the value and what its rounding left), so that the sum over the keys
-// sees 32-bit weights; O stays in registers.
-constexpr int TC_ROWS = 64, TC_KEYS = 64, TC_MAX_D = 128;
+// product rounded to bfloat16 (as the cached values are); O stays in float32 registers.
+constexpr int TC_ROWS = 64, TC_KEYS = 64;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -374,17 +373,13 @@ gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ 
         const float w = gate_weight(sc[nt][c], scale, cap, two_over_cap, bias[c >> 1]);
         sc[nt][c] = (edge && (key > qpos[c >> 1] || key > k_last)) || qpos[c >> 1] < 0 ? 0.f : w;
       }
-    // O += P V, P as two bfloat16 parts
+    // O += P V: the 32-bit weights enter the product rounded to bfloat16, as the values they multiply are
 #pragma unroll
     for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
-      uint32_t hi[4], lo[4];
+      uint32_t pf[4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const float a = sc[2 * ks + (r >> 1)][(r & 1) * 2], b = sc[2 * ks + (r >> 1)][(r & 1) * 2 + 1];
-        const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
-        hi[r] = *reinterpret_cast<const uint32_t*>(&h2);
-        lo[r] = pack_bf16(a - __low2float(h2), b - __high2float(h2));
-      }
+      for (int r = 0; r < 4; ++r)
+        pf[r] = pack_bf16(sc[2 * ks + (r >> 1)][(r & 1) * 2], sc[2 * ks + (r >> 1)][(r & 1) * 2 + 1]);
 #pragma unroll
       for (int np = 0; np < DV / 16; ++np) {
         // two value tiles (16 columns) at a time: four 8x8 matrices, transposed on the way in
@@ -393,10 +388,8 @@ gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ 
         const uint32_t addr = (uint32_t)__cvta_generic_to_shared(at);
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
-        mma_bf16(o[2 * np], hi, b0, b1);
-        mma_bf16(o[2 * np], lo, b0, b1);
-        mma_bf16(o[2 * np + 1], hi, b2, b3);
-        mma_bf16(o[2 * np + 1], lo, b2, b3);
+        mma_bf16(o[2 * np], pf, b0, b1);
+        mma_bf16(o[2 * np + 1], pf, b2, b3);
       }
     }
   }

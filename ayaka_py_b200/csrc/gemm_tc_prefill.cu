@@ -83,6 +83,10 @@ struct PrefillArgs {
   // lane per column, so that an instruction writes one run of up to 128 contiguous bytes whatever the rows'
   // alignment, where a thread that owns a row would store 32 separate elements.  No residual in this form.
   int turned;
+  // Grouped form: the weight holds several matrices of N rows one after the other, and the rows of every
+  // 128-row tile of X belong to one of them: w_rows[m tile] is the weight row at which that tile's matrix
+  // starts (written by a kernel earlier in the stream).  Null: one matrix.
+  const int* w_rows;
 };
 
 // Where the keys of row `row` go: element offset of the row's place in a cache tensor, or -1 (a row
@@ -357,19 +361,23 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       // A cursor walks this CTA's tiles and their K blocks; no division or modulo per K block
       // (one thread issues every copy, and its arithmetic set the pace of the whole pipeline).
       const int total_it = my_tiles * my_kb;
-      struct Cursor { int tile, kx, m0, n0, kb; };
+      struct Cursor { int tile, kx, m0, n0, kb; };       // n0: the tile's first weight row
+      auto weight_row = [&](int tile) {
+        return (args.w_rows && tile < total_tiles) ? args.w_rows[tile / args.n_tiles] : 0;
+      };
       auto start = [&]() {
         Cursor c; c.tile = first_tile; c.kb = kb_first; c.kx = kb_first * BLOCK_K;
-        c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN;
+        c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN + weight_row(c.tile);
         return c;
       };
       auto advance = [&](Cursor& c) {
         c.kx += BLOCK_K;
         if (++c.kb == kb_last) {
           c.kb = kb_first; c.kx = kb_first * BLOCK_K; c.tile += tile_step;
-          c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN;
+          c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN + weight_row(c.tile);
         }
       };
+      if (args.w_rows) pdl_wait();                  // which matrix a tile reads was decided by a kernel before this one
       // The weight does not depend on the kernels before this one: its first
       // stages start streaming at once; the rows X wait for the predecessor.
       const int pre = min(STAGES, total_it);
@@ -1264,3 +1272,51 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
   return ayk_check_launch("ayk_gemm_tc_prefill");
 }
 }  // namespace
+
+
+// Grouped product: X [M, K] in tiles of 128 rows, each tile's rows multiplied by the matrix that starts at
+// weight row w_rows[tile] of W [w_total_rows, K] (matrices of N rows one after the other); C [M, N], bfloat16
+// or float32, no bias, activation or residual.  M is a multiple of 128.  Whole tiles only (no split along K).
+AYK_EXPORT int ayk_gemm_tc_prefill_grouped(void* C, const void* X, const void* W, const int* w_rows, int M, int N, int K,
+                                           int w_total_rows, int out_dtype, int sms, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  AYK_REQUIRE(M % BM == 0 && K % 8 == 0 && w_rows != nullptr, "ayk_gemm_tc_prefill_grouped: rows in whole tiles of %d, K a multiple of 8", BM);
+  AYK_REQUIRE((uintptr_t)X % 16 == 0 && (uintptr_t)W % 16 == 0 && (uintptr_t)C % 16 == 0, "ayk_gemm_tc_prefill_grouped: operands must be 16-byte aligned");
+  if (sms <= 0) sms = ayk_sm_count();
+  const int BN = ayk_gemm_tc_prefill_tile_k(M, N, K, sms, out_dtype == AYK_DTYPE_F32);
+  AYK_REQUIRE(BN >= 32 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill_grouped: tile width %d", BN);
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (setup() != 0) return -1;
+  }
+  CUtensorMap mx, mw;
+  if (encode(&mx, X, M, K, BM) != 0) return -1;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    MapKey key{W, w_total_rows, K, BN};
+    auto it = g_weight_maps.find(key);
+    if (it == g_weight_maps.end()) {
+      if (encode(&mw, W, w_total_rows, K, BN) != 0) return -1;
+      g_weight_maps.emplace(key, mw);
+    } else {
+      mw = it->second;
+    }
+  }
+  PrefillArgs args{};
+  args.C = C; args.error = g_error_dev;
+  args.M = M; args.N = N; args.K = K; args.act = AYK_ACT_NONE; args.out_bf16 = out_dtype == AYK_DTYPE_BF16;
+  args.BN = BN;
+  args.vec_ok = N % 8 == 0;
+  args.mode = epilogue_mode(AYK_ACT_NONE, false, args.out_bf16);
+  args.box_m = BM;
+  args.m_tiles = M / BM;
+  args.n_tiles = (N + BN - 1) / BN;
+  const int stages = SMEM_TILES / (A_BYTES + BN * BLOCK_K * 2);
+  args.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+  args.splits = 1;
+  args.w_rows = w_rows;
+  const int total = args.m_tiles * args.n_tiles;
+  CUtensorMap mr = mx, mc = mx;
+  ayk_launch(gemm_tc_prefill_kernel, dim3(total < sms ? total : sms), dim3(THREADS), SMEM_BYTES, stream, mx, mw, mr, mc, args);
+  return ayk_check_launch("ayk_gemm_tc_prefill_grouped");
+}

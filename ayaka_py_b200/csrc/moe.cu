@@ -113,6 +113,56 @@ moe_plan_kernel(int* __restrict__ sorted, int* __restrict__ tiles, const int* __
   }
 }
 
+// The plan for the product that runs on tcgen05 (gemm_tc_prefill, grouped form): every expert's pairs
+// start at a multiple of PAD_ROWS rows, so that each 128-row tile of the gathered rows belongs to one
+// expert.  row_of_pair[p]: the pair's row in that layout; w_rows1 / w_rows2 [max_tiles]: per tile the first
+// weight row of its expert in the two stacked weights (n1 and n2 rows per expert; 0 for tiles past the end).
+constexpr int PAD_ROWS = 128;
+
+__global__ void __launch_bounds__(1024)
+moe_plan_padded_kernel(int* __restrict__ row_of_pair, int* __restrict__ w_rows1, int* __restrict__ w_rows2,
+                       const int* __restrict__ ids, int P, int E, int n1, int n2, int max_tiles) {
+  extern __shared__ int sh[];
+  int* count = sh;          // [E]
+  int* start = sh + E;      // [E]
+  int* cursor = sh + 2 * E; // [E]
+  pdl_trigger();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+  pdl_wait();
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = n * PAD_ROWS;
+      for (int r = 0; r < count[e]; r += PAD_ROWS) {
+        if (n < max_tiles) { w_rows1[n] = e * n1; w_rows2[n] = e * n2; }
+        ++n;
+      }
+    }
+    for (; n < max_tiles; ++n) { w_rows1[n] = 0; w_rows2[n] = 0; }
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = ids[p];
+    row_of_pair[p] = start[e] + atomicAdd(&cursor[e], 1);     // a row's result does not depend on its place
+  }
+}
+
+// out[row_of_pair[p], :] = in[p / top, :], bfloat16 rows of d elements (d a multiple of 8); a warp per pair.
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ in, long long in_stride,
+                  const int* __restrict__ row_of_pair, int P, int top, int d) {
+  pdl_trigger();
+  pdl_wait();
+  const int p = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (p >= P) return;
+  const uint4* src = reinterpret_cast<const uint4*>(in + (size_t)(p / top) * in_stride);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row_of_pair[p] * d);
+  for (int i = lane; i < d / 8; i += 32) dst[i] = src[i];
+}
+
 // --------------------------------------------------------- grouped product --
 // out[o(s), n] = sum_k a[r(s), k] * w[expert, n, k] over the sorted rows s of a tile; w holds N_w
 // rows per expert.  GLU: w rows [0, N) are the gate, [N, 2N) the up projection, and the output is
@@ -310,28 +360,31 @@ moe_gemm_mma_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, lo
 
 // ------------------------------------------------- activation and weighted sum --
 // out[t, c] = act(in[t, c], in[t, n + c]) for the dense (shared) expert.
-template <typename O>
+template <typename I, typename O>
 __global__ void __launch_bounds__(256)
-glu_limited_kernel(O* __restrict__ out, const float* __restrict__ in, long long stride, int n, float limit, float slope) {
+glu_limited_kernel(O* __restrict__ out, const I* __restrict__ in, long long stride, int n, float limit, float slope) {
   pdl_trigger();
   pdl_wait();
-  const float* row = in + (size_t)blockIdx.x * stride;
+  const I* row = in + (size_t)blockIdx.x * stride;
   for (int c = threadIdx.x; c < n; c += blockDim.x)
-    out[(size_t)blockIdx.x * n + c] = from_float<O>(glu_limited(row[c], row[n + c], limit, slope));
+    out[(size_t)blockIdx.x * n + c] = from_float<O>(glu_limited(to_float<I>(row[c]), to_float<I>(row[n + c]), limit, slope));
 }
 
-// shared[t, :] = sum_k weights[t, k] * picked[t * top + k, :] + sigmoid(mix[t]) * shared[t, :], the
-// chosen experts in the order of their choice.
+// shared[t, :] = sum_k weights[t, k] * picked[row of pair t * top + k, :] + sigmoid(mix[t]) * shared[t, :], the
+// chosen experts in the order of their choice; row_of_pair null: the pair's own number.
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(float* __restrict__ shared, const float* __restrict__ picked, const float* __restrict__ weights,
-                   const float* __restrict__ mix, long long mix_stride, int top, int d) {
+moe_combine_kernel(float* __restrict__ shared, const float* __restrict__ picked, const int* __restrict__ row_of_pair,
+                   const float* __restrict__ weights, const float* __restrict__ mix, long long mix_stride, int top, int d) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   const float gate = mix ? sigmoidf(mix[(size_t)t * mix_stride]) : 1.0f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float s = 0.f;
-    for (int k = 0; k < top; ++k) s = fmaf(weights[(size_t)t * top + k], picked[((size_t)t * top + k) * d + c], s);
+    for (int k = 0; k < top; ++k) {
+      const size_t pair = (size_t)t * top + k;
+      s = fmaf(weights[pair], picked[(size_t)(row_of_pair ? row_of_pair[pair] : pair) * d + c], s);
+    }
     shared[(size_t)t * d + c] = fmaf(gate, shared[(size_t)t * d + c], s);
   }
 }
@@ -385,21 +438,41 @@ AYK_EXPORT int ayk_moe_gemm(void* out, const void* a, long long a_stride, const 
   return ayk_check_launch("ayk_moe_gemm");
 }
 
-AYK_EXPORT int ayk_glu_limited(void* out, const float* in, long long stride, int T, int n, float limit, float slope,
-                               int out_dtype, cudaStream_t stream) {
+AYK_EXPORT int ayk_glu_limited(void* out, const void* in, long long stride, int T, int n, float limit, float slope,
+                               int in_dtype, int out_dtype, cudaStream_t stream) {
   if (T == 0 || n == 0) return 0;
-  if (out_dtype == AYK_DTYPE_F32)
-    ayk_launch(glu_limited_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)out, in, stride, n, limit, slope);
-  else if (out_dtype == AYK_DTYPE_BF16)
-    ayk_launch(glu_limited_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, in, stride, n, limit, slope);
+  if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32)
+    ayk_launch(glu_limited_kernel<float, float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)in, stride, n, limit, slope);
+  else if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(glu_limited_kernel<float, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)in,
+               stride, n, limit, slope);
+  else if (in_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(glu_limited_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out,
+               (const __nv_bfloat16*)in, stride, n, limit, slope);
   else
-    return ayk_fail("ayk_glu_limited: unknown dtype %d", out_dtype);
+    return ayk_fail("ayk_glu_limited: dtypes %d -> %d", in_dtype, out_dtype);
   return ayk_check_launch("ayk_glu_limited");
 }
 
-AYK_EXPORT int ayk_moe_combine(float* shared, const float* picked, const float* weights, const float* mix,
-                               long long mix_stride, int T, int top, int d, cudaStream_t stream) {
+AYK_EXPORT int ayk_moe_pad_rows() { return PAD_ROWS; }
+
+// The padded plan (see moe_plan_padded_kernel) and the gathered rows: gathered [max_tiles * 128, d] bfloat16 gets
+// row p / top of ``in`` at row_of_pair[p].  Two launches.
+AYK_EXPORT int ayk_moe_plan_padded(int* row_of_pair, int* w_rows1, int* w_rows2, void* gathered, const int* ids,
+                                   const void* in, long long in_stride, int T, int E, int top, int d, int n1, int n2,
+                                   int max_tiles, cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(E <= 4096 && d % 8 == 0 && in_stride % 8 == 0, "ayk_moe_plan_padded: %d experts, rows of %d", E, d);
+  ayk_launch(moe_plan_padded_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), stream, row_of_pair, w_rows1, w_rows2, ids,
+             T * top, E, n1, n2, max_tiles);
+  ayk_launch(moe_gather_kernel, dim3((T * top + 7) / 8), dim3(256), 0, stream, (__nv_bfloat16*)gathered, (const __nv_bfloat16*)in,
+             in_stride, (const int*)row_of_pair, T * top, top, d);
+  return ayk_check_launch("ayk_moe_plan_padded");
+}
+
+AYK_EXPORT int ayk_moe_combine(float* shared, const float* picked, const int* row_of_pair, const float* weights,
+                               const float* mix, long long mix_stride, int T, int top, int d, cudaStream_t stream) {
   if (T == 0 || d == 0) return 0;
-  ayk_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, shared, picked, weights, mix, mix_stride, top, d);
+  ayk_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, shared, picked, row_of_pair, weights, mix, mix_stride, top, d);
   return ayk_check_launch("ayk_moe_combine");
 }

@@ -148,72 +148,78 @@ struct RglruGate {
   }
 };
 
-// A block takes 32 neighbouring channels of one request; its warps take consecutive segments
-// of the request's rows.  With one warp the rows are walked once.  With several, every warp
-// first folds its segment into (A, B) with S_end = A S_begin + B, the warps' begins follow from
-// the request's state by walking the folds in order, and every warp then walks its segment
-// again from its true begin and writes the outputs.  The state is at state + slot * slot_stride + c.
-constexpr int SCAN_WARPS = 16;
+// A block takes 32 neighbouring channels of one request and walks the request's rows in spans of
+// WARPS x SEG rows: every warp takes SEG consecutive rows of the span, computes their gates once
+// into registers (independent loads and transcendentals, nothing waits on the recurrence) and folds
+// them into (A, B) with S_end = A S_begin + B; the warps' begins follow from the state at the span's
+// start by walking the folds in order; every warp then replays its rows from its true begin out of
+// the registers and writes the outputs.  The state is at state + slot * slot_stride + c.
+constexpr int SEG = 8;
 
-template <typename O, typename Gate>
-__global__ void __launch_bounds__(SCAN_WARPS * 32)
+template <typename O, typename Gate, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 scan_kernel(O* __restrict__ out, float* __restrict__ state, long long slot_stride, Gate gate,
             const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int W) {
-  __shared__ float fold_a[SCAN_WARPS][32], fold_b[SCAN_WARPS][32];
+  __shared__ float fold_a[WARPS][32], fold_b[WARPS][32];
   pdl_trigger();
   const int req = blockIdx.y;
   const int first = req_q_start[req], end = req_q_start[req + 1];
   float* st = state + (size_t)req_slot[req] * slot_stride;
   pdl_wait();
-  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * 32 + lane;
   const bool live = c < W;
-  const int rows = end - first;
-  const int per = (rows + warps - 1) / warps;
-  const int lo = min(end, first + warp * per), hi = min(end, lo + per);
-  float S = 0.f;
-  if (warps > 1) {
+  float carry = live ? st[c] : 0.f;                     // the state at the start of the span
+  for (int span = first; span < end; span += WARPS * SEG) {
+    const int lo = span + warp * SEG;
+    Step s[SEG];
     float A = 1.f, B = 0.f;
-    if (live) {
-      for (int t = lo; t < hi; ++t) {
-        const Step s = gate(t, c);
-        A *= s.a;
-        B = fmaf(s.a, B, s.b);
+#pragma unroll
+    for (int i = 0; i < SEG; ++i) {
+      if (live && lo + i < end) s[i] = gate(lo + i, c);
+      else s[i] = Step{1.f, 0.f, 0.f};
+      A *= s[i].a;
+      B = fmaf(s[i].a, B, s[i].b);
+    }
+    float S = carry;
+    if (WARPS > 1) {
+      fold_a[warp][lane] = A;
+      fold_b[warp][lane] = B;
+      __syncthreads();
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        if (w == warp) S = carry;                       // this warp's begin: the folds before it applied
+        carry = fmaf(fold_a[w][lane], carry, fold_b[w][lane]);
       }
+      __syncthreads();                                  // the folds are read before the next span writes them
+    } else {
+      carry = fmaf(A, carry, B);
     }
-    fold_a[warp][lane] = A;
-    fold_b[warp][lane] = B;
-    __syncthreads();
-    if (live) {
-      S = st[c];
-      for (int w = 0; w < warp; ++w) S = fmaf(fold_a[w][lane], S, fold_b[w][lane]);
+#pragma unroll
+    for (int i = 0; i < SEG; ++i) {
+      S = fmaf(s[i].a, S, s[i].b);
+      if (live && lo + i < end) out[(size_t)(lo + i) * W + c] = from_float<O>(S * s[i].m);
     }
-    __syncthreads();       // every warp has read the state before the last one writes it
-  } else if (live) {
-    S = st[c];
   }
-  if (!live) return;
-  for (int t = lo; t < hi; ++t) {
-    const Step s = gate(t, c);
-    S = fmaf(s.a, S, s.b);
-    out[(size_t)t * W + c] = from_float<O>(S * s.m);
-  }
-  if (warp == warps - 1) st[c] = S;       // the last segment ends at the request's last row (or is empty after it)
+  if (live && warp == 0) st[c] = carry;
 }
 
 template <typename Gate>
 int launch_scan(void* out, float* state, long long slot_stride, const Gate& gate, const int* req_q_start,
                 const int* req_slot, int R, int W, int max_q_len, int out_dtype, cudaStream_t stream, const char* what) {
-  // a warp per 32 channels for short portions; 16 segments from 64 rows on
-  const int warps = max_q_len >= 64 ? SCAN_WARPS : (max_q_len >= 16 ? 4 : 1);
-  dim3 grid((W + 31) / 32, R), block(warps * 32);
-  if (out_dtype == AYK_DTYPE_F32)
-    ayk_launch(scan_kernel<float, Gate>, grid, block, 0, stream, (float*)out, state, slot_stride, gate, req_q_start, req_slot, W);
-  else if (out_dtype == AYK_DTYPE_BF16)
-    ayk_launch(scan_kernel<__nv_bfloat16, Gate>, grid, block, 0, stream, (__nv_bfloat16*)out, state, slot_stride, gate,
-               req_q_start, req_slot, W);
-  else
+  dim3 grid((W + 31) / 32, R);
+#define AYK_SCAN(O, WARPS)                                                                                              \
+  ayk_launch(scan_kernel<O, Gate, WARPS>, grid, dim3(WARPS * 32), 0, stream, (O*)out, state, slot_stride, gate, req_q_start, \
+             req_slot, W)
+  // a warp per 32 channels for single tokens and short portions; 16 warps (spans of 128 rows) from 64 rows on
+  if (out_dtype == AYK_DTYPE_F32) {
+    if (max_q_len >= 64) AYK_SCAN(float, 16); else if (max_q_len > SEG) AYK_SCAN(float, 4); else AYK_SCAN(float, 1);
+  } else if (out_dtype == AYK_DTYPE_BF16) {
+    if (max_q_len >= 64) AYK_SCAN(__nv_bfloat16, 16); else if (max_q_len > SEG) AYK_SCAN(__nv_bfloat16, 4); else AYK_SCAN(__nv_bfloat16, 1);
+  } else {
     return ayk_fail("%s: unknown dtype %d", what, out_dtype);
+  }
+#undef AYK_SCAN
   return ayk_check_launch(what);
 }
 

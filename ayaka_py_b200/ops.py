@@ -717,24 +717,66 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | Non
 
 def glu_limited(x: torch.Tensor, n: int, limit: float, slope: float, out_dtype: torch.dtype) -> torch.Tensor:
     """min(g, limit) sigmoid(slope g) (clamp(u, -limit, limit) + 1) with g = x[:, :n] and u = x[:, n:2n]
-    of float32 rows."""
+    of float32 or bfloat16 rows; the arithmetic is 32-bit."""
     lib = _ready()
-    if x.dtype != torch.float32 or x.stride(1) != 1 or x.shape[1] < 2 * n:
-        raise KernelError("glu_limited: float32 rows of at least 2 n columns")
+    if x.stride(1) != 1 or x.shape[1] < 2 * n:
+        raise KernelError("glu_limited: rows of at least 2 n columns")
     out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
     _launch(lib.ayk_glu_limited(_ptr(out), _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_int(x.shape[0]), ctypes.c_int(n),
-                                ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_int(_tag(out_dtype)), _stream()))
+                                ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_int(_tag(x.dtype)),
+                                ctypes.c_int(_tag(out_dtype)), _stream()))
     return out
 
 
-def moe_combine(picked: torch.Tensor, route: MoeRoute, shared: torch.Tensor, mix: torch.Tensor | None) -> torch.Tensor:
-    """shared[t] = sum_k weights[t, k] picked[t * top + k] + sigmoid(mix[t]) shared[t], in place; float32."""
+MOE_TENSOR_PAIRS = 64         # (token, choice) pairs from which the experts' products run on tcgen05
+
+
+def moe_experts_tc(h: torch.Tensor, in_weight: torch.Tensor, down_weight: torch.Tensor, route: MoeRoute, limit: float,
+                   slope: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """The experts of a step on tcgen05 (bfloat16): the pairs' rows are gathered expert by expert, every expert's
+    starting at a multiple of 128 rows, and the two products run as grouped forms of the many-row kernel, each
+    128-row tile against the matrix of its expert.  in_weight [experts, 2 inner, width] gate over up,
+    down_weight [experts, width, inner].  Returns (float32 rows [padded, width], row of every pair)."""
+    lib = _ready()
+    E, n1, d = in_weight.shape
+    inner = n1 // 2
+    T = h.shape[0]
+    pairs = T * route.top
+    pad = int(lib.ayk_moe_pad_rows())
+    max_tiles = pairs // pad + E
+    dev_ = h.device
+    row_of_pair = torch.empty((pairs,), dtype=torch.int32, device=dev_)
+    w_rows = torch.empty((2, max_tiles), dtype=torch.int32, device=dev_)
+    gathered = torch.empty((max_tiles * pad, d), dtype=torch.bfloat16, device=dev_)
+    _launch(lib.ayk_moe_plan_padded(_ptr(row_of_pair), _ptr(w_rows[0]), _ptr(w_rows[1]), _ptr(gathered), _ptr(route.ids), _ptr(h),
+                                    ctypes.c_longlong(h.stride(0)), ctypes.c_int(T), ctypes.c_int(E), ctypes.c_int(route.top),
+                                    ctypes.c_int(d), ctypes.c_int(n1), ctypes.c_int(d), ctypes.c_int(max_tiles), _stream()))
+    global launches
+    launches += 1
+    both = torch.empty((max_tiles * pad, n1), dtype=torch.bfloat16, device=dev_)
+    _launch(lib.ayk_gemm_tc_prefill_grouped(_ptr(both), _ptr(gathered), _ptr(in_weight), _ptr(w_rows[0]), ctypes.c_int(max_tiles * pad),
+                                            ctypes.c_int(n1), ctypes.c_int(d), ctypes.c_int(E * n1), ctypes.c_int(BF16),
+                                            ctypes.c_int(sm_count()), _stream()))
+    hidden = glu_limited(both, inner, limit, slope, torch.bfloat16)
+    picked = torch.empty((max_tiles * pad, d), dtype=torch.float32, device=dev_)
+    _launch(lib.ayk_gemm_tc_prefill_grouped(_ptr(picked), _ptr(hidden), _ptr(down_weight), _ptr(w_rows[1]), ctypes.c_int(max_tiles * pad),
+                                            ctypes.c_int(d), ctypes.c_int(inner), ctypes.c_int(E * d), ctypes.c_int(F32),
+                                            ctypes.c_int(sm_count()), _stream()))
+    return picked, row_of_pair
+
+
+def moe_combine(picked: torch.Tensor, route: MoeRoute, shared: torch.Tensor, mix: torch.Tensor | None,
+                row_of_pair: torch.Tensor | None = None) -> torch.Tensor:
+    """shared[t] = sum_k weights[t, k] picked[row of pair t * top + k] + sigmoid(mix[t]) shared[t], in place;
+    float32.  ``row_of_pair`` None: pair p lies at row p."""
     lib = _ready()
     _f32(picked, "picked"); _f32(shared, "shared")
     T, d = shared.shape
-    if picked.shape != (T * route.top, d) or (mix is not None and (mix.dtype != torch.float32 or mix.numel() != T)):
+    if picked.shape[1] != d or (row_of_pair is None and picked.shape[0] != T * route.top) or \
+            (mix is not None and (mix.dtype != torch.float32 or mix.numel() != T)):
         raise KernelError("moe_combine: rows do not fit")
-    _launch(lib.ayk_moe_combine(_ptr(shared), _ptr(picked), _ptr(route.weights), _ptr(mix),
+    _launch(lib.ayk_moe_combine(_ptr(shared), _ptr(picked), _ptr(None if row_of_pair is None else _i32(row_of_pair, "row_of_pair")),
+                                _ptr(route.weights), _ptr(mix),
                                 ctypes.c_longlong(mix.stride(0) if mix is not None else 0), ctypes.c_int(T),
                                 ctypes.c_int(route.top), ctypes.c_int(d), _stream()))
     return shared

@@ -10,7 +10,8 @@ token.
 The experts' matrices are kept stacked ([experts, 2 inner, width] with gate over up, and
 [experts, width, inner]); a step sorts its (token, choice) pairs by expert on the device and runs
 two grouped products over the sorted rows, so nothing about the routing comes back to the host
-(``csrc/moe.cu``).  The shared expert's gate, up and mixing row are one dense product."""
+(``csrc/moe.cu``): on tcgen05 for bfloat16 steps of many pairs (every expert's rows padded to whole
+128-row tiles), on mma.sync or the FP32 pipes otherwise.  The shared expert's gate, up and mixing row are one dense product."""
 
 from __future__ import annotations
 
@@ -34,6 +35,8 @@ class MoE(FeedForward):
             raise ValueError(f"top {top} of {experts} experts: the routing kernel picks 1 to 8")
         self.width, self.experts, self.top, self.inner, self.limit = width, experts, top, inner, float(limit)
         self.shared_inner, self.shared_limit, self.dtype = shared_inner, float(shared_limit), dtype
+        # many pairs in bfloat16, rows in whole 16-byte pieces: the experts' products run on tcgen05
+        self.tensor_cores = dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0
 
     def tensors(self):
         d, ff, sf = self.width, self.inner, self.shared_inner
@@ -71,12 +74,16 @@ class MoE(FeedForward):
         T, d, K = h.shape[0], self.width, self.top
         logits = ops.linear(h, self.router_weight, None, out_dtype=torch.float32)
         route = ops.moe_route(logits, self.experts, K)
-        hidden = ops.moe_gemm(h, self.in_weight, route, glu=(self.limit, self.GATE_SLOPE), out_dtype=self.dtype)
-        picked = ops.moe_gemm(hidden, self.down_weight, route, glu=None, out_dtype=torch.float32)          # [T * K, d]
+        rows = None
+        if self.tensor_cores and T * K >= ops.MOE_TENSOR_PAIRS:
+            picked, rows = ops.moe_experts_tc(h, self.in_weight, self.down_weight, route, self.limit, self.GATE_SLOPE)
+        else:
+            hidden = ops.moe_gemm(h, self.in_weight, route, glu=(self.limit, self.GATE_SLOPE), out_dtype=self.dtype)
+            picked = ops.moe_gemm(hidden, self.down_weight, route, glu=None, out_dtype=torch.float32)      # [T * K, d]
         sp = ops.linear(h, self.shared_in, None, out_dtype=torch.float32)
         sh = ops.glu_limited(sp, self.shared_inner, self.shared_limit, self.GATE_SLOPE, self.dtype)
         shared = ops.linear(sh, self.shared_down, None, out_dtype=torch.float32)
-        out = ops.moe_combine(picked, route, shared, sp[:, 2 * self.shared_inner])
+        out = ops.moe_combine(picked, route, shared, sp[:, 2 * self.shared_inner], rows)
         if residual is not None:
             residual.add_(out)
             return residual

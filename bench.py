@@ -35,7 +35,9 @@ operands.  ``--only rakalix`` measures the Rakalix design (latent attention and 
 layers in turn, PolyNorm feed-forward) beside GPT-2 at equal width, depth and inner
 width: a 2,048-token prefill step, decode steps of ``--batch`` requests, and each
 kernel of the design beside the like kernel of GPT-2 against its roofline; a JSON
-line per width.
+line per width.  ``--only luporax`` does the same for the Luporax design (recurrent, minGRU and
+sigmoid-attention layers with token shift, mixture-of-experts feed-forward) beside Rakalix,
+the closest model, at equal width, depth and active inner width.
 """
 
 from __future__ import annotations
@@ -624,6 +626,220 @@ def run_rakalix(width: int, layers: int, batch: int, steps: int, warmup: int, pk
     return result
 
 
+def luporax_document(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Luporax model of real-layer sizes: heads of 128 (four query heads to a key/value head), recurrent
+    layers as wide as the model in blocks of 128, 16 experts of which 2 run, their inner width and the
+    shared expert's adding up to 2.75 x the width per token."""
+    heads = width // 128
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": width, "limit": 7.0},
+           "shared": {"ff": width * 3 // 4, "limit": 7.0}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
+                     "scale": 128 ** -0.5, "softcap": 30.0}}
+    lru = {"type": "rglru", "mlp": mlp, "mixer": {"width": width, "blocks": heads, "conv": 4}}
+    gru = {"type": "mingru", "mlp": mlp, "mixer": {"width": width}}
+    return {"architecture": "Luporax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_scale": 1.0, "layers": [(lru, att, gru, att)[i % 4] for i in range(layers)]}
+
+
+def run_luporax(width: int, layers: int, batch: int, steps: int, warmup: int, pk: dict) -> dict:
+    """Luporax beside Rakalix at equal width, depth and active inner width (bfloat16, random weights): prefill
+    of 2 x 1,024 tokens in one step, decode of ``batch`` requests after 512-token prompts through the engine
+    (CUDA graphs), and the design's kernels one by one, timed as in ``run_rakalix``."""
+    import numpy as np
+    import torch
+
+    from ayaka_py_b200 import EngineConfig, Request, SamplingParams, StopCriteria, ops
+    from ayaka_py_b200.config.model import LuporaxConfig, RakalixConfig
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import random_model
+    from ayaka_py_b200.engine.step import StepEntry
+
+    vocab, heads = 32000, width // 128
+    configs = {"luporax": LuporaxConfig.from_dict(luporax_document(width, layers, vocab)),
+               "rakalix": RakalixConfig.from_dict(rakalix_document(width, layers, vocab))}
+    flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    rs = np.random.RandomState(3)
+
+    def timed(fn, reps=9):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        out = []
+        for _ in range(reps):
+            flush.fill_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return sorted(out)[len(out) // 2]
+
+    result = {"width": width, "layers": layers, "batch": batch}
+    kernels = []
+
+    def kernel(name, ms, gbytes=None, gflop=None, like=None):
+        row = {"kernel": name, "us": round(ms * 1e3, 1)}
+        if gbytes is not None:
+            row.update(gb_s=round(gbytes / (ms / 1e3), 1), frac=round(gbytes / (ms / 1e3) / pk["hbm_gbs"], 4), bound="hbm")
+        if gflop is not None:
+            row.update(tflops=round(gflop / ms, 2), frac=round(gflop / ms / pk["bf16_tflops"], 4), bound="bf16")
+        if like:
+            row["like"] = like
+        kernels.append(row)
+
+    for name, config in configs.items():
+        model = random_model(config, 1, "bfloat16", "cuda", generate_on_device=True)
+        engine = Engine(model, EngineConfig(dtype="bfloat16", kv_pages=batch * 64 + 130, page_size=16, max_requests=max(batch, 2),
+                                            batch_tokens=2048, prefill_chunk=2048, max_model_len=1024, decode_graph=True),
+                        eos_token_id=None)
+        cache, runner = engine.cache, engine.runner
+
+        def prefill_step():
+            slots = [cache.open(f"p{i}") for i in range(2)]
+            entries = [StepEntry(sl, 0, rs.randint(0, vocab, 1024).tolist(), [1023]) for sl in slots]
+            res = cache.reserve([(e.slot, 0, 1024) for e in entries])
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            runner.run(entries)
+            b.record()
+            torch.cuda.synchronize()
+            cache.commit(res)
+            for sl in slots:
+                cache.close(sl)
+            return a.elapsed_time(b)
+        times = [prefill_step() for _ in range(5)][2:]
+        prefill_ms = sorted(times)[1]
+
+        total_new = 2 * warmup + steps + 8
+        for i in range(batch):
+            engine.submit(Request(f"d{i}", rs.randint(0, vocab, PROMPT_LEN).tolist(), SamplingParams(temperature=0.0),
+                                  StopCriteria(max_tokens=total_new, ignore_eos=True)))
+        while any(st.computed < st.prompt_len for st in engine.scheduler.states.values()):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        a.record()
+        for _ in range(steps):
+            engine.step()
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        decode_ms = a.elapsed_time(b) / steps
+        weights = model.weight_bytes()
+        result[name] = {"prefill_tok_s": round(2048 / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                        "decode_tok_s": round(batch / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                        "decode_e2e_tok_s": round(batch * steps / wall, 1), "weight_gb": round(weights / 1e9, 3),
+                        "kv_bytes_per_token": cache.bytes_per_token()}
+        for rid in list(engine.scheduler.states):
+            engine.abort(rid)
+        engine.finished.clear()
+        if name != "luporax":
+            del engine, model
+            torch.cuda.empty_cache()
+            continue
+
+        # ---- the design's kernels alone, on the shapes of the two steps above
+        d, T = width, 2048
+        bf, f32 = torch.bfloat16, torch.float32
+        x = torch.randn(T, d, device="cuda")
+        pairs = 2 * (1024 * 1025 // 2)
+        ctx_len = PROMPT_LEN + 64
+        lru, att, gru = model.blocks[0], model.blocks[1], model.blocks[2]
+        bind = {"lru": model.bindings[0], "att": model.bindings[1], "gru": model.bindings[2]}
+
+        def open_step(lengths, starts=None):
+            slots = [cache.open(f"k{i}") for i in range(len(lengths))]
+            if starts:
+                res = cache.reserve([(sl, 0, st) for sl, st in zip(slots, starts)])
+                cache.commit(res)
+            res = cache.reserve([(sl, int(cache.length[sl]), n) for sl, n in zip(slots, lengths)])
+            ctx = runner.prepare([StepEntry(sl, int(cache.length[sl]), [0] * n, []) for sl, n in zip(slots, lengths)])
+            return ctx, res, slots
+
+        for label, lengths, starts in (("prefill", [1024, 1024], None), ("decode", [1] * batch, [ctx_len] * batch)):
+            ctx, res, slots = open_step(lengths, starts)
+            rows = ctx.num_rows
+            xr = x[:rows].contiguous()
+            W = width
+            ms = timed(lambda: lru.shift.forward(xr, ctx, bind["lru"]["shift"]))
+            kernel(f"token shift ({label})", ms, gbytes=rows * d * 6 / 1e9, like="rmsnorm + time conv")
+            y = torch.randn(rows, d, device="cuda")
+            ms = timed(lambda: lru.norm1.add_normed(xr, y))
+            kernel(f"rmsnorm + residual ({label})", ms, gbytes=rows * d * 12 / 1e9, like="rmsnorm + residual")
+            # recurrences
+            proj = torch.randn(rows, 3 * W, device="cuda")
+            st = cache.state_layer(bind["gru"]["mixer"].group, bind["gru"]["mixer"].layer)
+            ms = timed(lambda: ops.mingru_scan(proj, st, ctx, W, bf))
+            kernel(f"minGRU scan ({label})", ms, gbytes=rows * W * 14 / 1e9, like="hgrn2 recurrence")
+            mx = lru.mixer
+            st = cache.state_layer(bind["lru"]["mixer"].group, bind["lru"]["mixer"].layer)
+            ms = timed(lambda: ops.causal_conv(proj[:, W:2 * W], mx.conv_taps, mx.conv_bias, st, ctx))
+            kernel(f"causal conv + state ({label})", ms, gbytes=rows * W * 8 / 1e9, like="rmsnorm + time conv")
+            u = torch.randn(rows, W, device="cuda")
+            gates = torch.empty(rows, mx.blocks, 2 * (W // mx.blocks), device="cuda")
+            ms = timed(lambda: ops.head_matmul(u.view(rows, mx.blocks, W // mx.blocks), mx.gate_weight, gates))
+            kernel(f"per-block gate product K128 N256 ({label})", ms, gflop=2.0 * rows * W * 256 / 1e9, like="per-head product")
+            ms = timed(lambda: ops.rglru_scan(proj, u, gates, mx.gate_bias, mx.lam, st, ctx, W, mx.blocks, 8.0, bf))
+            kernel(f"RG-LRU scan ({label})", ms, gbytes=rows * W * 18 / 1e9, like="hgrn2 recurrence")
+            # attention
+            am = att.mixer
+            kp, vp = cache.kv_layer(bind["att"]["mixer"].group, bind["att"]["mixer"].layer)
+            table = ctx.tables[bind["att"]["mixer"].group]
+            G = am.kv_heads
+            aproj = torch.randn(rows, am.in_weight.shape[0], device="cuda")
+            ms = timed(lambda: ops.qk_norm_rotary(aproj, kp, vp, am.q_norm, am.k_norm, am.rotary.freq, am.rotary.dims, ctx, table,
+                                                  heads, 1e-6, True, bf))
+            kernel(f"qk norm + rotary + filing ({label})", ms, gbytes=rows * (heads + 2 * G) * 128 * 6 / 1e9, like="latent prepare")
+            q = torch.randn(rows, heads * 128, device="cuda").to(bf)
+            ms = timed(lambda: ops.sigmoid_attention(q, kp, vp, table, ctx, heads, am.scale, am.softcap, am.head_bias))
+            if label == "prefill":
+                kernel("sigmoid attention (prefill)", ms, gflop=pairs * heads * 2 * 256 / 1e9, like="latent attention")
+            else:
+                kernel("sigmoid attention + merge (decode)", ms, gbytes=batch * (ctx_len + 1) * G * 256 * 2 / 1e9, like="latent attention")
+            # experts
+            ff = lru.ffn
+            h = xr.to(bf)
+            logits = torch.randn(rows, 16, device="cuda")
+            ms = timed(lambda: ops.moe_route(logits, 16, 2))
+            kernel(f"routing + plan ({label})", ms)
+            route = ops.moe_route(logits, 16, 2)
+            touched = min(16, 2 * rows) * 2 * width * d * 2 / 1e9
+            if label == "prefill":
+                ms = timed(lambda: ops.moe_experts_tc(h, ff.in_weight, ff.down_weight, route, 7.0, 1.702))
+                kernel("experts on tcgen05: plan, gather, gate | up, activation, down (prefill)", ms,
+                       gflop=2.0 * 2 * rows * 3 * width * d / 1e9, like="linear + gelu")
+            else:
+                ms = timed(lambda: ops.moe_gemm(h, ff.in_weight, route, glu=(7.0, 1.702), out_dtype=bf))
+                kernel("grouped gate | up product + activation (decode)", ms, gbytes=touched, like="linear (decode)")
+                hidden = ops.moe_gemm(h, ff.in_weight, route, glu=(7.0, 1.702), out_dtype=bf)
+                ms = timed(lambda: ops.moe_gemm(hidden, ff.down_weight, route, glu=None, out_dtype=f32))
+                kernel("grouped down product (decode)", ms, gbytes=touched / 2, like="linear (decode)")
+            picked = torch.randn(2 * rows, d, device="cuda")
+            shared = torch.randn(rows, d, device="cuda")
+            sp = torch.randn(rows, ff.shared_in.shape[0], device="cuda")
+            ms = timed(lambda: ops.moe_combine(picked, route, shared, sp[:, 2 * ff.shared_inner]))
+            kernel(f"weighted sum of experts ({label})", ms, gbytes=rows * d * 16 / 1e9, like="rmsnorm + residual")
+            ms = timed(lambda: ops.glu_limited(sp, ff.shared_inner, 7.0, 1.702, bf))
+            kernel(f"gated activation ({label})", ms, gbytes=rows * ff.shared_inner * 10 / 1e9, like="polynorm")
+            cache.rollback(res)
+            for sl in slots:
+                cache.close(sl)
+        del engine, model
+        torch.cuda.empty_cache()
+    result["kernels"] = kernels
+    result["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    return result
+
+
 def reference_line(args) -> dict:
     """The reference arm: same shape, batch, prompt length and step counts, the reference's own engine."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -673,8 +889,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-graph", action="store_true", help="run decode steps eagerly")
     parser.add_argument("--no-points", action="store_true", help="only the decode steps at --batch")
-    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix: the model widths to measure")
-    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix"),
+    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix or luporax: the model widths to measure")
+    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix", "luporax"),
                         help="run one workload alone and print its numbers (for profiling): the 2,048-token prefill "
                              "step, the small shape's continuous batching, the large shape's mixed steps, or the four "
                              "products of an XL layer over row counts beside the library's matmul")
@@ -701,6 +917,11 @@ def main() -> int:
         for width in (int(w) for w in args.widths.split(",")):
             layers = 4 if args.layers == XL["n_layer"] else args.layers
             print(json.dumps({"rakalix_beside_gpt2": run_rakalix(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
+        return 0
+    if args.only == "luporax":
+        for width in (int(w) for w in args.widths.split(",")):
+            layers = 4 if args.layers == XL["n_layer"] else args.layers
+            print(json.dumps({"luporax_beside_rakalix": run_luporax(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
         return 0
     if args.only == "products":
         for row in run_products():
