@@ -230,7 +230,8 @@ gated_attention_kernel(T* __restrict__ out, float* __restrict__ partial, const T
 // bfloat16, head sizes in multiples of 16 up to 128.  The rows of a tile are (token, query head of
 // one key/value head) pairs, token-major: a block of four warps holds 64 of them (16 per warp), so the
 // query heads that share a key/value head also share its loads, in prompts and in single-token steps
-// alike.  Keys come 64 at a time through shared memory.  S = Q K^T with mma.sync m16n8k16 (float32
+// alike.  Keys and values come 64 at a time through two buffers of shared memory, the next tile copied
+// asynchronously under the products of this one.  S = Q K^T with mma.sync m16n8k16 (float32
 // sums); the weights are computed in 32-bit in the registers of S's fragments and enter the second
 // product rounded to bfloat16 (as the cached values are); O stays in float32 registers.
 constexpr int TC_ROWS = 64, TC_KEYS = 64;
@@ -253,27 +254,33 @@ __device__ __forceinline__ float gate_weight(float s, float scale, float cap, fl
   return __fdividef(1.0f, 1.0f + __expf(-(s + bias)));
 }
 
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;                    // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
 template <int D, int DV>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                            const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
                            const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ table, int table_stride,
                            const int* __restrict__ req_q_start, const int* __restrict__ req_pos0, int num_req,
-                           int total_rows, int H, int Hkv, int page_size, float scale, float cap,
+                           int total_rows, int H, int Hkv, int page_shift, float scale, float cap,
                            const float* __restrict__ head_bias, int part_keys, int tq) {
   constexpr int LDK = D + 8, LDV = DV + 8;
+  constexpr int TILE = TC_KEYS * (LDK + LDV);          // elements of one buffer: keys, then values
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [TC_KEYS][LDK]; the queries pass through here first
-  __nv_bfloat16* Vs = Ks + TC_KEYS * LDK;                             // [TC_KEYS][LDV]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // two buffers; the queries pass through the second first
   pdl_trigger();
   pdl_wait();
   const int hpg = H / Hkv;
   int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
   for (int r = 0; r < num_req; ++r) {
     int len = req_q_start[r + 1] - req_q_start[r];
-    int tiles = (len + tq - 1) / tq;
-    if (tile < tiles) { req = r; q0 = tile * tq; q_len = len; break; }
-    tile -= tiles;
+    int n = (len + tq - 1) / tq;
+    if (tile < n) { req = r; q0 = tile * tq; q_len = len; break; }
+    tile -= n;
   }
   if (req < 0) return;
   const int g = blockIdx.y;
@@ -288,9 +295,34 @@ gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ 
   if (k_first > last_pos) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
   const int* my_table = table + (size_t)req * table_stride;
+  const int page_mask = (1 << page_shift) - 1;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
-  // queries -> shared memory -> A fragments of this warp's 16 rows
+  // A tile of 64 keys and their values, copied asynchronously in 16-byte pieces; pieces of keys beyond the
+  // part, or on the padding page, are filled with zeros.
+  auto fetch = [&](int k0, int buf) {
+    __nv_bfloat16* Kd = tiles + buf * TILE;
+    __nv_bfloat16* Vd = Kd + TC_KEYS * LDK;
+    for (int i = tid; i < TC_KEYS * (D / 8); i += 128) {
+      const int j = i / (D / 8), piece = i - j * (D / 8);
+      const int kp = k0 + j;
+      const int page = kp <= k_last ? my_table[kp >> page_shift] : 0;
+      const size_t cell = (((size_t)max(page, 0) << page_shift) + (kp & page_mask)) * Hkv + g;
+      cp_async_16(Kd + j * LDK + piece * 8, kcache + cell * D + piece * 8, page > 0);
+    }
+    for (int i = tid; i < TC_KEYS * (DV / 8); i += 128) {
+      const int j = i / (DV / 8), piece = i - j * (DV / 8);
+      const int kp = k0 + j;
+      const int page = kp <= k_last ? my_table[kp >> page_shift] : 0;
+      const size_t cell = (((size_t)max(page, 0) << page_shift) + (kp & page_mask)) * Hkv + g;
+      cp_async_16(Vd + j * LDV + piece * 8, vcache + cell * DV + piece * 8, page > 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(k_first, 0);
+
+  // queries -> shared memory (the second buffer) -> A fragments of this warp's 16 rows
+  __nv_bfloat16* Qs = tiles + TILE;
   for (int i = tid; i < TC_ROWS * (D / 8); i += 128) {
     const int m = i / (D / 8), piece = i - m * (D / 8);
     uint4 v = zero4;
@@ -298,18 +330,19 @@ gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ 
       const int tok = m / hpg, head = g * hpg + (m - tok * hpg);
       v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + tok) * H + head) * D + piece * 8);
     }
-    *reinterpret_cast<uint4*>(Ks + m * LDK + piece * 8) = v;
+    *reinterpret_cast<uint4*>(Qs + m * LDK + piece * 8) = v;
   }
   __syncthreads();
   uint32_t qf[D / 16][4];
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
-    const __nv_bfloat16* base = Ks + (warp * 16 + gid) * LDK + ks * 16 + tig * 2;
+    const __nv_bfloat16* base = Qs + (warp * 16 + gid) * LDK + ks * 16 + tig * 2;
     qf[ks][0] = *reinterpret_cast<const uint32_t*>(base);
     qf[ks][1] = *reinterpret_cast<const uint32_t*>(base + 8 * LDK);
     qf[ks][2] = *reinterpret_cast<const uint32_t*>(base + 8);
     qf[ks][3] = *reinterpret_cast<const uint32_t*>(base + 8 * LDK + 8);
   }
+  __syncthreads();                                     // the queries are in registers: the second buffer is free
   // this thread's two rows: their positions and their heads' biases
   int qpos[2];
   float bias[2];
@@ -327,30 +360,20 @@ gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ 
     for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
   const float two_over_cap = cap > 0.f ? 2.0f / cap : 0.f;
 
-  for (int k0 = k_first; k0 <= k_last; k0 += TC_KEYS) {
-    __syncthreads();                                   // the fragments of the tile before (or the queries) are read
-    for (int i = tid; i < TC_KEYS * (D / 8); i += 128) {
-      const int j = i / (D / 8), piece = i - j * (D / 8);
-      const int kp = k0 + j;
-      uint4 v = zero4;
-      if (kp <= k_last) {
-        const int page = my_table[kp / page_size];
-        if (page > 0) v = *reinterpret_cast<const uint4*>(kcache + (((size_t)page * page_size + (kp % page_size)) * Hkv + g) * D + piece * 8);
-      }
-      *reinterpret_cast<uint4*>(Ks + j * LDK + piece * 8) = v;
-    }
-    for (int i = tid; i < TC_KEYS * (DV / 8); i += 128) {
-      const int j = i / (DV / 8), piece = i - j * (DV / 8);
-      const int kp = k0 + j;
-      uint4 v = zero4;
-      if (kp <= k_last) {
-        const int page = my_table[kp / page_size];
-        if (page > 0) v = *reinterpret_cast<const uint4*>(vcache + (((size_t)page * page_size + (kp % page_size)) * Hkv + g) * DV + piece * 8);
-      }
-      *reinterpret_cast<uint4*>(Vs + j * LDV + piece * 8) = v;
+  int buf = 0;
+  for (int k0 = k_first; k0 <= k_last; k0 += TC_KEYS, buf ^= 1) {
+    // the next tile streams into the other buffer (read last an iteration ago, behind the barrier below)
+    const bool more = k0 + TC_KEYS <= k_last;
+    if (more) {
+      fetch(k0 + TC_KEYS, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (warp * 16 >= rows) continue;                   // a warp without live rows only helps with the loads
+    const __nv_bfloat16* Ks = tiles + buf * TILE;
+    const __nv_bfloat16* Vs = Ks + TC_KEYS * LDK;
+    if (warp * 16 < rows) {                            // a warp without live rows only helps with the loads
 
     // S = Q K^T: 8 tiles of 8 keys
     float sc[TC_KEYS / 8][4];
@@ -392,6 +415,8 @@ gated_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ 
         mma_bf16(o[2 * np + 1], pf, b2, b3);
       }
     }
+    }
+    __syncthreads();                                   // this buffer is refilled by the fetch after the next
   }
 
 #pragma unroll
@@ -476,13 +501,23 @@ AYK_EXPORT int ayk_gated_attention(void* out, float* partial, const void* q, con
                                                                      (D == 64 && Dv == 128) || (D == 128 && Dv == 64) ||
                                                                      (D == 32 && Dv == 32) || (D == 16 && Dv == 16))) {
     const int tq = TC_ROWS / hpg;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    AYK_REQUIRE((1 << page_shift) == page_size, "ayk_gated_attention: pages of %d tokens are no power of two", page_size);
     dim3 grid(total_rows / tq + num_req, Hkv, parts);
 #define AYK_GATED(DD, DDV)                                                                                                  \
   if (D == DD && Dv == DDV) {                                                                                               \
-    const size_t smem = (size_t)TC_KEYS * (DD + 8 + DDV + 8) * sizeof(__nv_bfloat16);                                       \
+    const size_t smem = (size_t)2 * TC_KEYS * (DD + 8 + DDV + 8) * sizeof(__nv_bfloat16);                                   \
+    static AykPerDevice granted;                                                                                            \
+    if (!granted.here()) {                                                                                                  \
+      cudaError_t e = cudaFuncSetAttribute(gated_attention_mma_kernel<DD, DDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                                                      \
+      if (e != cudaSuccess) return ayk_fail("ayk_gated_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));     \
+      granted.here() = true;                                                                                                \
+    }                                                                                                                       \
     ayk_launch(gated_attention_mma_kernel<DD, DDV>, grid, dim3(128), smem, stream, (__nv_bfloat16*)out, partial,            \
                (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table, table_stride,    \
-               req_q_start, req_pos0, num_req, total_rows, H, Hkv, page_size, scale, cap, head_bias, pk, tq);               \
+               req_q_start, req_pos0, num_req, total_rows, H, Hkv, page_shift, scale, cap, head_bias, pk, tq);              \
   }
     AYK_GATED(64, 64) AYK_GATED(128, 128) AYK_GATED(64, 128) AYK_GATED(128, 64) AYK_GATED(32, 32) AYK_GATED(16, 16)
 #undef AYK_GATED

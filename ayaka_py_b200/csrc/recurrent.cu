@@ -11,7 +11,6 @@
 
 namespace {
 
-__device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // ------------------------------------------------------------- token shift --
@@ -108,18 +107,43 @@ struct Step {
   float a, b, m;
 };
 
+// The transcendentals of the gates: the library's functions where the rows are stored in 32-bit, the
+// hardware's approximations (ex2, lg2, rcp: a few ulp in 32-bit) where they are stored in bfloat16 and the
+// gates' cost in issue slots is what bounds the scan.
+template <bool FAST>
+struct GateMath {
+  static __device__ __forceinline__ float exp(float z) { return FAST ? __expf(z) : expf(z); }
+  static __device__ __forceinline__ float sigmoid(float z) {
+    return FAST ? __fdividef(1.0f, 1.0f + __expf(-z)) : 1.0f / (1.0f + expf(-z));
+  }
+  static __device__ __forceinline__ float gelu(float z) {
+    return FAST ? apply_activation_tc<AYK_ACT_GELU_TANH>(z, AYK_ACT_GELU_TANH) : apply_activation(z, AYK_ACT_GELU_TANH);
+  }
+  // sqrt(1 - exp(2 l)) for l <= 0, without cancellation where l is close to 0
+  static __device__ __forceinline__ float root_one_minus_square(float l) {
+    if (!FAST) return sqrtf(-expm1f(2.0f * l));
+    const float t = 2.0f * l;
+    // -expm1(t): the series near zero, 1 - e^t elsewhere
+    const float v = t > -0.0625f ? -t * (1.0f + t * (0.5f + t * (0.16666667f + t * 0.041666668f))) : 1.0f - __expf(t);
+    return sqrtf(v);
+  }
+};
+
 // minGRU over projection rows [z | u | g] (biases already added).
 struct MinGruGate {
   const float* proj;
   long long stride;
   int W;
-  __device__ __forceinline__ Step operator()(int t, int c) const {
+  __device__ __forceinline__ float prepare(int) const { return 0.f; }
+  template <bool FAST>
+  __device__ __forceinline__ Step at(int t, int c, float) const {
+    typedef GateMath<FAST> M;
     const float* row = proj + (size_t)t * stride;
-    const float z = sigmoidf(row[c]);
+    const float z = M::sigmoid(row[c]);
     const float u = row[W + c];
-    const float cand = u >= 0.f ? u + 0.5f : sigmoidf(u);
+    const float cand = u >= 0.f ? u + 0.5f : M::sigmoid(u);
     const float g = row[2 * W + c];
-    return {1.0f - z, z * cand, g * sigmoidf(g)};
+    return {1.0f - z, z * cand, g * M::sigmoid(g)};
   }
 };
 
@@ -134,17 +158,20 @@ struct RglruGate {
   const float* lam;
   int W, block;      // channels per block
   float decay;
-  __device__ __forceinline__ Step operator()(int t, int c) const {
+  // per channel, once: -decay * softplus(lam)
+  __device__ __forceinline__ float prepare(int c) const { return -decay * softplusf(lam[c]); }
+  template <bool FAST>
+  __device__ __forceinline__ Step at(int t, int c, float rate) const {
+    typedef GateMath<FAST> M;
     const int b = c / block, j = c - b * block;
     const size_t at = (size_t)b * 2 * block + j;
     const float* g = gates + (size_t)t * 2 * W;
-    const float r = sigmoidf(g[at] + gate_bias[at]);
-    const float i = sigmoidf(g[at + block] + gate_bias[at + block]);
-    const float log_a = -decay * r * softplusf(lam[c]);
-    const float a = expf(log_a);
+    const float r = M::sigmoid(g[at] + gate_bias[at]);
+    const float i = M::sigmoid(g[at + block] + gate_bias[at + block]);
+    const float log_a = rate * r;
     // 1 - a^2 = -expm1(2 log a): no cancellation where a is close to 1
-    const float in = sqrtf(-expm1f(2.0f * log_a)) * i * u[(size_t)t * W + c];
-    return {a, in, apply_activation(proj[(size_t)t * stride + c], AYK_ACT_GELU_TANH)};
+    const float in = M::root_one_minus_square(log_a) * i * u[(size_t)t * W + c];
+    return {M::exp(log_a), in, M::gelu(proj[(size_t)t * stride + c])};
   }
 };
 
@@ -169,6 +196,8 @@ scan_kernel(O* __restrict__ out, float* __restrict__ state, long long slot_strid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * 32 + lane;
   const bool live = c < W;
+  constexpr bool FAST = sizeof(O) == 2;
+  const float per_channel = live ? gate.prepare(c) : 0.f;
   float carry = live ? st[c] : 0.f;                     // the state at the start of the span
   for (int span = first; span < end; span += WARPS * SEG) {
     const int lo = span + warp * SEG;
@@ -176,7 +205,7 @@ scan_kernel(O* __restrict__ out, float* __restrict__ state, long long slot_strid
     float A = 1.f, B = 0.f;
 #pragma unroll
     for (int i = 0; i < SEG; ++i) {
-      if (live && lo + i < end) s[i] = gate(lo + i, c);
+      if (live && lo + i < end) s[i] = gate.template at<FAST>(lo + i, c, per_channel);
       else s[i] = Step{1.f, 0.f, 0.f};
       A *= s[i].a;
       B = fmaf(s[i].a, B, s[i].b);
@@ -211,11 +240,11 @@ int launch_scan(void* out, float* state, long long slot_stride, const Gate& gate
 #define AYK_SCAN(O, WARPS)                                                                                              \
   ayk_launch(scan_kernel<O, Gate, WARPS>, grid, dim3(WARPS * 32), 0, stream, (O*)out, state, slot_stride, gate, req_q_start, \
              req_slot, W)
-  // a warp per 32 channels for single tokens and short portions; 16 warps (spans of 128 rows) from 64 rows on
+  // a warp per 32 channels for single tokens and short portions; 32 warps (spans of 256 rows) from 128 rows on
   if (out_dtype == AYK_DTYPE_F32) {
-    if (max_q_len >= 64) AYK_SCAN(float, 16); else if (max_q_len > SEG) AYK_SCAN(float, 4); else AYK_SCAN(float, 1);
+    if (max_q_len >= 128) AYK_SCAN(float, 32); else if (max_q_len > SEG) AYK_SCAN(float, 4); else AYK_SCAN(float, 1);
   } else if (out_dtype == AYK_DTYPE_BF16) {
-    if (max_q_len >= 64) AYK_SCAN(__nv_bfloat16, 16); else if (max_q_len > SEG) AYK_SCAN(__nv_bfloat16, 4); else AYK_SCAN(__nv_bfloat16, 1);
+    if (max_q_len >= 128) AYK_SCAN(__nv_bfloat16, 32); else if (max_q_len > SEG) AYK_SCAN(__nv_bfloat16, 4); else AYK_SCAN(__nv_bfloat16, 1);
   } else {
     return ayk_fail("%s: unknown dtype %d", what, out_dtype);
   }
