@@ -358,6 +358,78 @@ moe_gemm_mma_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, lo
     }
 }
 
+// --------------------------------------------- few pairs: matrix times vector --
+// A step of single tokens has a handful of (token, choice) pairs, most on experts of their own: each pair
+// then streams its expert's matrix once, and the product is bound by that stream.  A block takes one pair and
+// 64 output features; the pair's activation row waits in shared memory as float32; a warp takes 8 features, two
+// at a time, its lanes striding along K in 16-byte pieces of the weight rows (with the activation, both the gate
+// row and the up row of a feature).  No sorting: pair p reads row p / top (gather) or p, and writes row p.
+constexpr int GV_COLS = 64;
+
+__device__ __forceinline__ float dot8(const uint4& w, const float4& x0, const float4& x1) {
+  // a bfloat16 is the upper half of a float
+  float s = __uint_as_float(w.x << 16) * x0.x;
+  s = fmaf(__uint_as_float(w.x & 0xffff0000u), x0.y, s);
+  s = fmaf(__uint_as_float(w.y << 16), x0.z, s);
+  s = fmaf(__uint_as_float(w.y & 0xffff0000u), x0.w, s);
+  s = fmaf(__uint_as_float(w.z << 16), x1.x, s);
+  s = fmaf(__uint_as_float(w.z & 0xffff0000u), x1.y, s);
+  s = fmaf(__uint_as_float(w.w << 16), x1.z, s);
+  return fmaf(__uint_as_float(w.w & 0xffff0000u), x1.w, s);
+}
+
+template <typename O, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, long long a_stride,
+                const __nv_bfloat16* __restrict__ w, const int* __restrict__ ids, int top, int gather, int N, int N_w,
+                int Kd, float limit, float slope) {
+  extern __shared__ __align__(16) float act[];          // [Kd]
+  pdl_trigger();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const __nv_bfloat16* arow = a + (size_t)(gather ? pair / top : pair) * a_stride;
+  for (int i = tid; i < Kd / 8; i += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(arow + i * 8);
+    float4 lo, hi;
+    lo.x = __uint_as_float(v.x << 16); lo.y = __uint_as_float(v.x & 0xffff0000u);
+    lo.z = __uint_as_float(v.y << 16); lo.w = __uint_as_float(v.y & 0xffff0000u);
+    hi.x = __uint_as_float(v.z << 16); hi.y = __uint_as_float(v.z & 0xffff0000u);
+    hi.z = __uint_as_float(v.w << 16); hi.w = __uint_as_float(v.w & 0xffff0000u);
+    *reinterpret_cast<float4*>(act + i * 8) = lo;
+    *reinterpret_cast<float4*>(act + i * 8 + 4) = hi;
+  }
+  __syncthreads();
+  const __nv_bfloat16* we = w + (size_t)ids[pair] * N_w * Kd;
+  const int first = blockIdx.y * GV_COLS + warp * 8;
+#pragma unroll 1
+  for (int j = 0; j < 8; j += 2) {
+    const int n0 = first + j, n1 = n0 + 1;               // warp-uniform
+    if (n0 >= N) break;
+    const bool two = n1 < N;
+    float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
+    const __nv_bfloat16* r0 = we + (size_t)n0 * Kd;
+    const __nv_bfloat16* r1 = we + (size_t)(two ? n1 : n0) * Kd;
+    for (int k = lane * 8; k < Kd; k += 256) {
+      const float4 x0 = *reinterpret_cast<const float4*>(act + k), x1 = *reinterpret_cast<const float4*>(act + k + 4);
+      const uint4 wa = *reinterpret_cast<const uint4*>(r0 + k), wb = *reinterpret_cast<const uint4*>(r1 + k);
+      if (GLU) {
+        const uint4 wc = *reinterpret_cast<const uint4*>(r0 + (size_t)N * Kd + k), wd = *reinterpret_cast<const uint4*>(r1 + (size_t)N * Kd + k);
+        u0 += dot8(wc, x0, x1);
+        u1 += dot8(wd, x0, x1);
+      }
+      g0 += dot8(wa, x0, x1);
+      g1 += dot8(wb, x0, x1);
+    }
+    g0 = warp_sum(g0); g1 = warp_sum(g1);
+    if (GLU) { u0 = warp_sum(u0); u1 = warp_sum(u1); }
+    if (lane == 0) {
+      out[(size_t)pair * N + n0] = from_float<O>(GLU ? glu_limited(g0, u0, limit, slope) : g0);
+      if (two) out[(size_t)pair * N + n1] = from_float<O>(GLU ? glu_limited(g1, u1, limit, slope) : g1);
+    }
+  }
+}
+
 // ------------------------------------------------- activation and weighted sum --
 // out[t, c] = act(in[t, c], in[t, n + c]) for the dense (shared) expert.
 template <typename I, typename O>
@@ -475,4 +547,24 @@ AYK_EXPORT int ayk_moe_combine(float* shared, const float* picked, const int* ro
   if (T == 0 || d == 0) return 0;
   ayk_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, shared, picked, row_of_pair, weights, mix, mix_stride, top, d);
   return ayk_check_launch("ayk_moe_combine");
+}
+
+// The products of a few pairs, pair by pair (see moe_gemv_kernel): bfloat16 a and w, K a multiple of 8 and at most
+// 12,288.  glu: out [pairs, N] bfloat16 = activation of (gate, up) rows of w [E, 2 N, K], a row p / top; else
+// out [pairs, N] float32 = a row p times w [E, N, K].
+AYK_EXPORT int ayk_moe_gemv_takes(int Kd, long long a_stride) { return Kd % 8 == 0 && a_stride % 8 == 0 && Kd <= 12288; }
+
+AYK_EXPORT int ayk_moe_gemv(void* out, const void* a, long long a_stride, const void* w, const int* ids, int pairs, int top,
+                            int N, int N_w, int Kd, int glu, float limit, float slope, cudaStream_t stream) {
+  if (pairs == 0 || N == 0) return 0;
+  AYK_REQUIRE(ayk_moe_gemv_takes(Kd, a_stride), "ayk_moe_gemv: rows of %d elements (stride %lld)", Kd, a_stride);
+  dim3 grid(pairs, (N + GV_COLS - 1) / GV_COLS);
+  const size_t smem = (size_t)Kd * sizeof(float);
+  if (glu)
+    ayk_launch(moe_gemv_kernel<__nv_bfloat16, true>, grid, dim3(256), smem, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a,
+               a_stride, (const __nv_bfloat16*)w, ids, top, 1, N, N_w, Kd, limit, slope);
+  else
+    ayk_launch(moe_gemv_kernel<float, false>, grid, dim3(256), smem, stream, (float*)out, (const __nv_bfloat16*)a, a_stride,
+               (const __nv_bfloat16*)w, ids, top, 0, N, N_w, Kd, limit, slope);
+  return ayk_check_launch("ayk_moe_gemv");
 }

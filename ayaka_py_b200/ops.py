@@ -715,6 +715,30 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | Non
     return out
 
 
+def moe_gemv_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the pair-by-pair product takes these operands (bfloat16, rows in whole 16-byte pieces)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and bool(_ready().ayk_moe_gemv_takes(ctypes.c_int(w.shape[2]), ctypes.c_longlong(a.stride(0)))))
+
+
+def moe_gemv(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | None) -> torch.Tensor:
+    """The experts' product for a handful of pairs, each pair streaming its expert's matrix on its own: no
+    sorting, rows lie pair by pair (token-major).  ``glu`` = (limit, slope): a [T, K] tokens' rows, w
+    [experts, 2 N, K], bfloat16 activations [T * top, N]; None: a [T * top, K], w [experts, N, K], float32 out."""
+    lib = _ready()
+    E, n_w, K = w.shape
+    pairs = route.ids.numel()
+    N = n_w // 2 if glu is not None else n_w
+    if a.shape[1] != K or a.stride(1) != 1 or not w.is_contiguous() or not moe_gemv_takes(a, w):
+        raise KernelError("moe_gemv: operands do not fit")
+    out = torch.empty((pairs, N), dtype=torch.bfloat16 if glu is not None else torch.float32, device=a.device)
+    limit, slope = glu if glu is not None else (0.0, 0.0)
+    _launch(lib.ayk_moe_gemv(_ptr(out), _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), _ptr(route.ids), ctypes.c_int(pairs),
+                             ctypes.c_int(route.top), ctypes.c_int(N), ctypes.c_int(n_w), ctypes.c_int(K),
+                             ctypes.c_int(1 if glu is not None else 0), ctypes.c_float(limit), ctypes.c_float(slope), _stream()))
+    return out
+
+
 def glu_limited(x: torch.Tensor, n: int, limit: float, slope: float, out_dtype: torch.dtype) -> torch.Tensor:
     """min(g, limit) sigmoid(slope g) (clamp(u, -limit, limit) + 1) with g = x[:, :n] and u = x[:, n:2n]
     of float32 or bfloat16 rows; the arithmetic is 32-bit."""

@@ -11,7 +11,8 @@ The experts' matrices are kept stacked ([experts, 2 inner, width] with gate over
 [experts, width, inner]); a step sorts its (token, choice) pairs by expert on the device and runs
 two grouped products over the sorted rows, so nothing about the routing comes back to the host
 (``csrc/moe.cu``): on tcgen05 for bfloat16 steps of many pairs (every expert's rows padded to whole
-128-row tiles), on mma.sync or the FP32 pipes otherwise.  The shared expert's gate, up and mixing row are one dense product."""
+128-row tiles), pair by pair as matrix-vector products for a handful of pairs, on mma.sync or the
+FP32 pipes otherwise.  The shared expert's gate, up and mixing row are one dense product."""
 
 from __future__ import annotations
 
@@ -77,6 +78,10 @@ class MoE(FeedForward):
         rows = None
         if self.tensor_cores and T * K >= ops.MOE_TENSOR_PAIRS:
             picked, rows = ops.moe_experts_tc(h, self.in_weight, self.down_weight, route, self.limit, self.GATE_SLOPE)
+        elif self.tensor_cores and ops.moe_gemv_takes(h, self.in_weight):
+            # a handful of pairs (a step of single tokens): every pair streams its expert's matrices on its own
+            hidden = ops.moe_gemv(h, self.in_weight, route, glu=(self.limit, self.GATE_SLOPE))
+            picked = ops.moe_gemv(hidden, self.down_weight, route, glu=None)                               # [T * K, d]
         else:
             hidden = ops.moe_gemm(h, self.in_weight, route, glu=(self.limit, self.GATE_SLOPE), out_dtype=self.dtype)
             picked = ops.moe_gemm(hidden, self.down_weight, route, glu=None, out_dtype=torch.float32)      # [T * K, d]

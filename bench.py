@@ -818,11 +818,15 @@ def run_luporax(width: int, layers: int, batch: int, steps: int, warmup: int, pk
                 kernel("experts on tcgen05: plan, gather, gate | up, activation, down (prefill)", ms,
                        gflop=2.0 * 2 * rows * 3 * width * d / 1e9, like="linear + gelu")
             else:
+                touched = 2 * rows * 2 * width * d * 2 / 1e9          # every pair streams its expert's rows
+                ms = timed(lambda: ops.moe_gemv(h, ff.in_weight, route, glu=(7.0, 1.702)))
+                kernel("experts' gate | up product + activation, pair by pair (decode)", ms, gbytes=touched, like="linear (decode)")
+                hidden = ops.moe_gemv(h, ff.in_weight, route, glu=(7.0, 1.702))
+                ms = timed(lambda: ops.moe_gemv(hidden, ff.down_weight, route, glu=None))
+                kernel("experts' down product, pair by pair (decode)", ms, gbytes=touched / 2, like="linear (decode)")
                 ms = timed(lambda: ops.moe_gemm(h, ff.in_weight, route, glu=(7.0, 1.702), out_dtype=bf))
-                kernel("grouped gate | up product + activation (decode)", ms, gbytes=touched, like="linear (decode)")
-                hidden = ops.moe_gemm(h, ff.in_weight, route, glu=(7.0, 1.702), out_dtype=bf)
-                ms = timed(lambda: ops.moe_gemm(hidden, ff.down_weight, route, glu=None, out_dtype=f32))
-                kernel("grouped down product (decode)", ms, gbytes=touched / 2, like="linear (decode)")
+                kernel("grouped gate | up product + activation on mma.sync (decode; not the path taken)", ms,
+                       gbytes=min(16, 2 * rows) * 2 * width * d * 2 / 1e9, like="linear (decode)")
             picked = torch.randn(2 * rows, d, device="cuda")
             shared = torch.randn(rows, d, device="cuda")
             sp = torch.randn(rows, ff.shared_in.shape[0], device="cuda")
