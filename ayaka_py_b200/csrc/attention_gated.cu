@@ -22,13 +22,13 @@ __device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(
 constexpr int MAX_ROT_HALF = 128;
 
 template <typename C>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 qk_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __restrict__ vpages, const float* __restrict__ proj,
                   long long stride, const float* __restrict__ qw, const float* __restrict__ kw,
                   const float* __restrict__ freq, int rot_dims, const int* __restrict__ row_req,
                   const int* __restrict__ positions, const int* __restrict__ table, int table_stride, int page_size,
                   int H, int G, int D, int Dv, float eps, int writes) {
-  __shared__ float red[8];
+  __shared__ float red[32];                 // the warps' sums: queries in [0, 16), keys in [16, 32)
   __shared__ float cs[MAX_ROT_HALF], sn[MAX_ROT_HALF];
   pdl_trigger();
   const int t = blockIdx.x;
@@ -47,10 +47,12 @@ qk_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __restrict__ 
   sq = warp_sum(sq);
   sk = warp_sum(sk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { red[warp] = sq; red[4 + warp] = sk; }
+  if (lane == 0) { red[warp] = sq; red[16 + warp] = sk; }
   __syncthreads();
-  const float inv_q = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)nq + eps);
-  const float inv_k = 1.0f / sqrtf(((red[4] + red[5]) + (red[6] + red[7])) / (float)nk + eps);
+  float tq = 0.f, tk = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { tq += red[w]; tk += red[16 + w]; }      // the same order in every thread
+  const float inv_q = 1.0f / sqrtf(tq / (float)nq + eps);
+  const float inv_k = 1.0f / sqrtf(tk / (float)nk + eps);
 
   C* qdst = qout + (size_t)t * nq;
   for (int i = threadIdx.x; i < nq; i += blockDim.x) {
@@ -465,11 +467,13 @@ AYK_EXPORT int ayk_qk_norm_rotary(void* qout, void* kpages, void* vpages, const 
   if (T == 0) return 0;
   AYK_REQUIRE(rot_dims % 2 == 0 && rot_dims <= D && rot_dims / 2 <= MAX_ROT_HALF,
               "ayk_qk_norm_rotary: %d rotated dimensions do not fit a head of %d (at most %d)", rot_dims, D, 2 * MAX_ROT_HALF);
+  // a row of a few thousand elements takes more warps (up to 16): with few rows in a step nothing else hides the loads
+  const int threads = H * D >= 2048 ? 512 : (H * D >= 1024 ? 256 : 128);
   if (dtype == AYK_DTYPE_F32)
-    ayk_launch(qk_prepare_kernel<float>, dim3(T), dim3(128), 0, stream, (float*)qout, (float*)kpages, (float*)vpages, proj,
+    ayk_launch(qk_prepare_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)qout, (float*)kpages, (float*)vpages, proj,
                stride, qw, kw, freq, rot_dims, row_req, positions, table, table_stride, page_size, H, G, D, Dv, eps, writes);
   else if (dtype == AYK_DTYPE_BF16)
-    ayk_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (__nv_bfloat16*)qout, (__nv_bfloat16*)kpages,
+    ayk_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)qout, (__nv_bfloat16*)kpages,
                (__nv_bfloat16*)vpages, proj, stride, qw, kw, freq, rot_dims, row_req, positions, table, table_stride,
                page_size, H, G, D, Dv, eps, writes);
   else
