@@ -470,6 +470,29 @@ def test_tensor_core_sigmoid_attention_against_the_32_bit_pipes(H, G, D, Dv, P):
         cache.commit(res)
 
 
+@pytest.mark.parametrize("d,E,top,ff,T", [(128, 16, 2, 64, 6), (64, 4, 3, 128, 40), (256, 8, 1, 96, 300)])
+def test_the_experts_products_agree_on_every_path(d, E, top, ff, T):
+    """bfloat16: the grouped tcgen05 form (pairs padded to 128-row tiles per expert), the pair-by-pair
+    matrix-vector kernel, the mma.sync tiles and the FP32 pipes (on float32 copies) from one routing."""
+    from ayaka_py_b200 import ops
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    h = torch.randn(T, d, generator=gen, device="cuda").to(torch.bfloat16)
+    w1 = (torch.randn(E, 2 * ff, d, generator=gen, device="cuda") / d ** 0.5).to(torch.bfloat16)
+    w2 = (torch.randn(E, d, ff, generator=gen, device="cuda") / ff ** 0.5).to(torch.bfloat16)
+    route = ops.moe_route(torch.randn(T, E, generator=gen, device="cuda") * 3, E, top)
+    act = (1.5, 1.702)
+    hidden32 = ops.moe_gemm(h.float(), w1.float(), route, glu=act, out_dtype=torch.float32)
+    want = ops.moe_gemm(hidden32, w2.float(), route, glu=None, out_dtype=torch.float32)          # [T * top, d], pair by pair
+    tiles = ops.moe_gemm(ops.moe_gemm(h, w1, route, glu=act, out_dtype=torch.bfloat16), w2, route, glu=None, out_dtype=torch.float32)
+    by_pair = ops.moe_gemv(ops.moe_gemv(h, w1, route, glu=act), w2, route, glu=None)
+    padded, rows = ops.moe_experts_tc(h, w1, w2, route, *act)
+    scale = float(want.abs().max())
+    for name, got in (("mma.sync tiles", tiles), ("pair by pair", by_pair), ("tcgen05 grouped", padded[rows.long()])):
+        assert not torch.isnan(got).any(), name
+        assert float((got - want).abs().max()) < 0.02 * scale, (name, float((got - want).abs().max()), scale)
+    assert ops.tc_error() == 0
+
+
 # --------------------------------------------------------------- whole models --
 
 def test_layers_one_by_one_in_32_bit(models):
