@@ -269,8 +269,8 @@ class LuporaxConfig(ModelConfig):
                 _require_int(source, f"layers[{i}].weights_of", minimum=0)
                 if source >= i or "weights_of" in self.layers[source]:
                     raise ConfigError(f"layers[{i}].weights_of must name an earlier layer that has tensors of its own")
-                mine = {k: v for k, v in layer.items() if k != "weights_of"}
-                if json.dumps(mine, sort_keys=True) != json.dumps(dict(self.layers[source]), sort_keys=True):
+                theirs = self.layers[source]
+                if layer["type"] != theirs["type"] or dict(mixer) != dict(theirs["mixer"]) or layer.get("mlp") != theirs.get("mlp"):
                     raise ConfigError(f"layers[{i}] runs layer {source}'s tensors but describes another layer")
             mlp = layer.get("mlp")
             if mlp is not None:

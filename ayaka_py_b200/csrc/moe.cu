@@ -23,7 +23,7 @@ __device__ __forceinline__ float glu_limited(float g, float u, float limit, floa
   return g * sigmoidf(slope * g) * (u + 1.0f);
 }
 
-constexpr int MAX_TOP = 8;
+constexpr int MAX_TOP = 16;
 constexpr int TILE_ROWS = 32;
 
 // ------------------------------------------------------------------- route --

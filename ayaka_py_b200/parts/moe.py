@@ -32,8 +32,8 @@ class MoE(FeedForward):
 
     def __init__(self, width: int, experts: int, top: int, inner: int, limit: float, shared_inner: int,
                  shared_limit: float, dtype=torch.float32, device="cuda"):
-        if not 1 <= top <= min(experts, 8):
-            raise ValueError(f"top {top} of {experts} experts: the routing kernel picks 1 to 8")
+        if not 1 <= top <= min(experts, 16):
+            raise ValueError(f"top {top} of {experts} experts: the routing kernel picks 1 to 16")
         self.width, self.experts, self.top, self.inner, self.limit = width, experts, top, inner, float(limit)
         self.shared_inner, self.shared_limit, self.dtype = shared_inner, float(shared_limit), dtype
         # many pairs in bfloat16, rows in whole 16-byte pieces: the experts' products run on tcgen05

@@ -68,9 +68,9 @@ CONFIG_B = {"architecture": "Luporax", "vocab": 130, "width": 64, "norm": {"eps"
                        attention(3, 3, 16, 40, 16, 500.0, 0.3, 5.0, None), rglru(40, 5, 6, None)]}
 # C: sizes of the tensor-core kernels (heads of 64, one key/value head for eight query heads, widths in
 # multiples of 8), sixteen experts of which four are chosen.
-_C0 = attention(8, 1, 64, 64, 32, 10000.0, 0.125, 30.0, moe(16, 4, 64, 2.0, 128, 1.5))
+_C0 = attention(8, 1, 64, 64, 32, 20000.0, 0.11, 25.0, moe(16, 4, 64, 2.5, 120, 1.25))
 CONFIG_C = {"architecture": "Luporax", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
-            "logit_scale": 0.25, "layers": [_C0, rglru(256, 4, 4, moe(16, 4, 64, 2.0, 128, 1.5)), mingru(192, None), again(_C0, 0)]}
+            "logit_scale": 0.2, "layers": [_C0, rglru(192, 3, 4, moe(16, 4, 64, 2.5, 120, 1.25)), mingru(160, None), again(_C0, 0)]}
 CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
 LENGTHS = {"A": [1, 2, 19, 77, 150], "B": [3, 33, 64, 129], "C": [5, 48, 100, 300]}
 PAGE = {"A": 16, "B": 8, "C": 16}
